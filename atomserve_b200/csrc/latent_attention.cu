@@ -147,6 +147,7 @@ struct LatentParams {
   int QT, GC, HC;            // tokens per tile, heads per block, head chunks
   int PS, NP;
   float scale;
+  int window;                // > 0: a query at p sees keys j with p - j < window only
 };
 
 template <typename T, int EPL>
@@ -180,7 +181,8 @@ latent_attention_kernel(const LatentParams p) {
 
   const int hi = pos0 + nq;  // exclusive
   const int part = blockIdx.z;
-  const int key_lo = part * p.PS;
+  // with a window no row of the tile sees a key before pos0 - window + 1 (pages before it may be gone)
+  const int key_lo = max(part * p.PS, p.window > 0 ? pos0 - p.window + 1 : 0);
   const int key_hi = (int)min((long long)hi, (long long)(part + 1) * p.PS);
 
   for (int i = threadIdx.x; i < num_rows * Dk; i += blockDim.x) {
@@ -220,7 +222,7 @@ latent_attention_kernel(const LatentParams p) {
       const int rr = warp + s * kWarps;
       if (rr >= num_rows) break;
       const int pq = pos0 + rr / gc;
-      const bool visible = in_range && j <= pq;
+      const bool visible = in_range && j <= pq && (p.window <= 0 || pq - j < p.window);
       float score = -INFINITY;
       if (visible) {
         const float* qrow = q_s + rr * Dk;
@@ -335,7 +337,8 @@ extern "C" int asb_head_matmul(void* out, int out_f32, int out_row, int out_head
 extern "C" int asb_latent_attention(float* out, const float* q, const void* pages, const int* block_tables,
                                     const int* req_q_start, const int* req_pos_start, float* part_m, float* part_l,
                                     float* part_acc, int num_tokens, int R, int H, int rank, int rot, int bs,
-                                    int table_width, int PS, int NP, float scale, int dtype, cudaStream_t stream) {
+                                    int table_width, int PS, int NP, float scale, int window, int dtype,
+                                    cudaStream_t stream) {
   if (num_tokens == 0 || R == 0) return 0;
   if (rank < 1 || rank > 512) return asb::fail("latent_attention: latent size %d not in 1..512", rank);
   if (NP < 1 || PS < kKeyTile || PS % kKeyTile) return asb::fail("latent_attention: partition size %d must be a positive multiple of %d", PS, kKeyTile);
@@ -348,7 +351,7 @@ extern "C" int asb_latent_attention(float* out, const float* q, const void* page
   p.GC = H < kMaxRows ? H : kMaxRows;
   p.QT = kMaxRows / p.GC;
   p.HC = (H + p.GC - 1) / p.GC;
-  p.PS = PS; p.NP = NP; p.scale = scale;
+  p.PS = PS; p.NP = NP; p.scale = scale; p.window = window;
   if ((size_t)(kMaxRows * p.Dk + kKeyTile * (p.Dk | 1)) * 4 > 220 * 1024) return asb::fail("latent_attention: key width %d is too large", p.Dk);
   const int epl = (rank + 31) / 32;
 #define ASB_LAT_CASE(E) case E: ASB_DISPATCH_DTYPE(dtype, T, return launch_attention<T, E>(p, num_tokens, stream)); break;

@@ -40,6 +40,7 @@ struct LatentParams {
   int QT, GC, HC;
   int PS, NP;
   float scale;
+  int window;  // > 0: a query at p sees keys j with p - j < window only
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -106,7 +107,8 @@ latent_attention_mma_kernel(const LatentParams p) {
   const int gc = min(p.GC, p.H - head0);
   const int num_rows = nq * gc;  // row rr = qi * gc + g
   const int hi = pos0 + nq;
-  const int key_lo = blockIdx.z * p.PS;
+  // with a window no row of the tile sees a key before pos0 - window + 1 (pages before it may be gone)
+  const int key_lo = max((int)blockIdx.z * p.PS, p.window > 0 ? pos0 - p.window + 1 : 0);
   const int key_hi = (int)min((long long)hi, (long long)(blockIdx.z + 1) * p.PS);
 
   // queries as bfloat16, a warp per row, rows beyond the block's and columns beyond Dk zero
@@ -251,7 +253,7 @@ latent_attention_mma_kernel(const LatentParams p) {
           const int rr = i * 16 + g + (c >> 1) * 8;
           const int jj = warp * 8 + 2 * t + (c & 1);
           const int j = kt0 + jj;
-          const bool visible = j >= key_lo && j < key_hi && j <= row_pos[i][c >> 1];  // (no position for rows beyond the block's)
+          const bool visible = j >= key_lo && j < key_hi && j <= row_pos[i][c >> 1] && (p.window <= 0 || row_pos[i][c >> 1] - j < p.window);  // (no position for rows beyond the block's)
           s_s[rr * LDS + jj] = visible ? s[i][c] * p.scale : -INFINITY;
         }
     }
@@ -497,7 +499,7 @@ extern "C" void asb_latent_attention_mma_tile_shape(int H, int* QT, int* GC) {
 extern "C" int asb_latent_attention_mma(float* out, const float* q, const void* pages, const int* block_tables,
                                         const int* req_q_start, const int* req_pos_start, float* part_m, float* part_l,
                                         float* part_acc, int num_tokens, int R, int H, int rank, int rot, int bs,
-                                        int table_width, int PS, int NP, float scale, cudaStream_t stream) {
+                                        int table_width, int PS, int NP, float scale, int window, cudaStream_t stream) {
   if (num_tokens == 0 || R == 0) return 0;
   if (!asb_latent_attention_mma_supported(rank, rot)) return asb::fail("latent_attention_mma: latent %d + %d is not taken", rank, rot);
   if (NP < 1 || PS < KT || PS % KT) return asb::fail("latent_attention_mma: partition size %d must be a positive multiple of %d", PS, KT);
@@ -510,7 +512,7 @@ extern "C" int asb_latent_attention_mma(float* out, const float* q, const void* 
   p.bs = bs; p.table_width = table_width;
   asb_latent_attention_mma_tile_shape(H, &p.QT, &p.GC);
   p.HC = (H + p.GC - 1) / p.GC;
-  p.PS = PS; p.NP = NP; p.scale = scale;
+  p.PS = PS; p.NP = NP; p.scale = scale; p.window = window;
   const size_t smem = smem_bytes(p.LDK);
   if (rank <= 64) return launch_attention<1>(p, num_tokens, smem, stream);
   if (rank <= 128) return launch_attention<2>(p, num_tokens, smem, stream);

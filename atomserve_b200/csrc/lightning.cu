@@ -59,6 +59,7 @@ struct LightningParams {
   const float2* rot_table;  // [T, rot / 2] (cos, sin) of each token's angles, or null: no rotation
   int rot;
   float q_scale, k_scale;
+  int qk_share;             // this many neighbouring heads read one q and one k (grouped state-space layers); 1: a q and k per head
 };
 
 __device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
@@ -71,6 +72,7 @@ lightning_kernel(const LightningParams p) {
   const float* tok_gain = GEN ? p.tok_gain : nullptr;
   float* norm_state = GEN ? p.norm_state : nullptr;
   const float2* rot_table = GEN ? p.rot_table : nullptr;
+  const int hq = GEN ? (int)blockIdx.y / p.qk_share : (int)blockIdx.y;  // whose q and k columns this head reads
   asb::pdl_wait();
   asb::pdl_launch_dependents();
   extern __shared__ float smem[];
@@ -122,7 +124,7 @@ lightning_kernel(const LightningParams p) {
         const int t = i >> p.dp_shift, d = i - (t << p.dp_shift);
         qv[u] = kv[u] = qp[u] = kp[u] = 0.f;
         if (i < nt * DP && d < p.D) {
-          const T* row = proj + (size_t)(t0 + t) * p.stride + h * p.D + d;
+          const T* row = proj + (size_t)(t0 + t) * p.stride + hq * p.D + d;
           qv[u] = asb::to_float(row[p.q_off]);
           if (!p.carry) kv[u] = asb::to_float(row[p.k_off]);
           if (rot_table && d < p.rot) {  // the other entry of this one's pair
@@ -268,7 +270,7 @@ template <typename T, int RPT>
 int launch(const LightningParams& p, int R, cudaStream_t stream) {
   const int CPB = kThreads / p.DS;
   const size_t smem = sizeof(float) * (kTokenTile * (2 * p.DS * RPT + CPB) + p.DS * RPT);
-  const bool general = p.tok_decay || p.tok_gain || p.norm_state || p.rot_table || p.q_scale != 1.f || p.k_scale != 1.f;
+  const bool general = p.tok_decay || p.tok_gain || p.norm_state || p.rot_table || p.q_scale != 1.f || p.k_scale != 1.f || p.qk_share != 1;
   auto kern = general ? lightning_kernel<T, RPT, true> : lightning_kernel<T, RPT, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return asb::fail("lightning_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
@@ -364,13 +366,16 @@ extern "C" int asb_lightning_scan(float* local, float* state, const int* state_s
 
 // The general form. decay [H] or tok_decay [T, H] (one of them); tok_gain [T, H] or null;
 // norm_state [slots, H, D] with norm_out [T, H], or both null; rot_table [T, rot / 2, 2] (asb_rotary_table), or null.
-extern "C" int asb_linear_recurrence(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
-                                     float* state, const int* state_slots, const int* req_q_start,
-                                     const float* decay, const float* tok_decay, const float* tok_gain,
-                                     float* norm_state, float* norm_out, float* through, const float* rot_table,
-                                     int rot, float q_scale, float k_scale, int R, int H, int D, int V, int act,
-                                     int mode, int dtype, cudaStream_t stream) {
+// qk_share: every group of this many neighbouring heads shares one q and one k (H / qk_share heads
+// of D columns from q_off and k_off); the values, states and outputs stay per head.
+extern "C" int asb_linear_recurrence_shared(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
+                                            float* state, const int* state_slots, const int* req_q_start,
+                                            const float* decay, const float* tok_decay, const float* tok_gain,
+                                            float* norm_state, float* norm_out, float* through, const float* rot_table,
+                                            int rot, float q_scale, float k_scale, int R, int H, int D, int V, int act,
+                                            int mode, int qk_share, int dtype, cudaStream_t stream) {
   if (R == 0) return 0;
+  if (qk_share < 1 || H % qk_share) return asb::fail("linear_recurrence: %d heads do not share q and k in groups of %d", H, qk_share);
   if (H < 1 || D < 1 || V < 1 || H > 65535) return asb::fail("linear_recurrence: %d heads of %d x %d", H, D, V);
   if (!decay && !tok_decay) return asb::fail("linear_recurrence: no decay given");
   if ((norm_state == nullptr) != (norm_out == nullptr)) return asb::fail("linear_recurrence: a normaliser needs its state and its output");
@@ -382,7 +387,7 @@ extern "C" int asb_linear_recurrence(float* out, const void* proj, int stride, i
   p.tok_decay = tok_decay; p.tok_gain = tok_gain; p.norm_state = norm_state; p.norm_out = norm_out;
   p.through = (mode == 1 && tok_decay) ? through : nullptr;
   p.rot_table = (rot_table && rot > 0) ? reinterpret_cast<const float2*>(rot_table) : nullptr; p.rot = rot;
-  p.q_scale = q_scale; p.k_scale = k_scale;
+  p.q_scale = q_scale; p.k_scale = k_scale; p.qk_share = qk_share;
   p.zero_init = mode == 1;  // mode 0: the recurrence from the slots' states; 1: from zero, per segment; 2: the carried share
   p.carry = mode == 2;
   // rows of the state per thread: 64 from D = 64 on, fewer for narrow heads; D beyond 64 is
@@ -404,6 +409,17 @@ extern "C" int asb_linear_recurrence(float* out, const void* proj, int stride, i
     return launch<T, 16>(p, R, stream);
   });
   return 0;
+}
+
+extern "C" int asb_linear_recurrence(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,
+                                     float* state, const int* state_slots, const int* req_q_start,
+                                     const float* decay, const float* tok_decay, const float* tok_gain,
+                                     float* norm_state, float* norm_out, float* through, const float* rot_table,
+                                     int rot, float q_scale, float k_scale, int R, int H, int D, int V, int act,
+                                     int mode, int dtype, cudaStream_t stream) {
+  return asb_linear_recurrence_shared(out, proj, stride, q_off, k_off, v_off, state, state_slots, req_q_start, decay,
+                                      tok_decay, tok_gain, norm_state, norm_out, through, rot_table, rot, q_scale, k_scale,
+                                      R, H, D, V, act, mode, 1, dtype, stream);
 }
 
 extern "C" int asb_lightning_attention(float* out, const void* proj, int stride, int q_off, int k_off, int v_off,

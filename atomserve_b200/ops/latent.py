@@ -18,21 +18,21 @@ ATTENTION_KERNEL = os.environ.get("ATOMSERVE_B200_LATENT_ATTENTION", "mma")
 
 
 def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int | None, q_lat: torch.Tensor, pages: torch.Tensor | None,
-                   gain: torch.Tensor | None, inv_freq: torch.Tensor, positions: torch.Tensor,
+                   gain: torch.Tensor | None, inv_freq: torch.Tensor | None, positions: torch.Tensor,
                    slots: torch.Tensor | None, *, heads: int, dim: int, rank: int, rot: int, rot_dims: int,
                    eps: float) -> None:  # fmt: skip
     """Per token of proj [T, W]: with `pages` ([num_blocks, 1, block_size, rank + rot]), write
     [rms_norm(latent) * gain | turned shared key part] to the token's slot, the latent being the
     `rank` columns from kv_off and the key part the `rot` after them; and turn the last `rot` of
     each head's dim + rot query columns (from q_off) into q_lat[t, h, rank:] (float32). Of the
-    `rot` entries the first `rot_dims` turn, neighbours paired."""
+    `rot` entries the first `rot_dims` turn, neighbours paired (rot 0: no such part, no frequencies)."""
     require_cuda(proj, q_lat, pages, gain, inv_freq, positions, slots)
     if proj.dim() != 2 or not proj.is_contiguous():
         raise KernelLibraryError("latent_prepare: proj must be a contiguous [tokens, columns] tensor")
     T = proj.shape[0]
     if q_lat.dtype != torch.float32 or q_lat.shape != (T, heads, rank + rot) or not q_lat.is_contiguous():
         raise KernelLibraryError(f"latent_prepare: q_lat must be contiguous float32 [{T}, {heads}, {rank + rot}]")
-    if inv_freq.dtype != torch.float32 or inv_freq.shape != (rot_dims // 2,):
+    if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.shape != (rot_dims // 2,)):
         raise KernelLibraryError(f"latent_prepare: inv_freq must be float32 [{rot_dims // 2}]")
     if pages is not None:
         if pages.dtype != proj.dtype or pages.dim() != 4 or pages.shape[1] != 1 or pages.shape[3] != rank + rot or not pages.is_contiguous():
@@ -100,9 +100,10 @@ def plan_latent_partitions(num_tokens: int, num_requests: int, heads: int, max_c
 
 def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, req_q_start: torch.Tensor,
                      req_pos_start: torch.Tensor, *, rank: int, num_requests: int, max_context: int, scale: float,
-                     partitions: tuple[int, int] | None = None) -> torch.Tensor:  # fmt: skip
+                     partitions: tuple[int, int] | None = None, window: int | None = None) -> torch.Tensor:  # fmt: skip
     """Causal softmax attention of q_lat [T, H, rank + rot] (float32) over the requests' cached
-    [c | kr] vectors; returns sum_j p_j c_j as float32 [T, H, rank]."""
+    [c | kr] vectors; returns sum_j p_j c_j as float32 [T, H, rank]. With a `window` a query at
+    position p sees the keys j with 0 <= p - j < window."""
     require_cuda(q_lat, pages, block_tables, req_q_start, req_pos_start)
     T, H, Dk = q_lat.shape
     if q_lat.dtype != torch.float32 or not q_lat.is_contiguous() or pages.shape[3] != Dk or pages.shape[1] != 1:
@@ -111,6 +112,7 @@ def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: tor
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelLibraryError("latent_attention: index tensors must be contiguous int32")
     out = torch.empty(T, H, rank, device=q_lat.device, dtype=torch.float32)
+    win = int(window) if window else 0
     ps, np_ = partitions or plan_latent_partitions(T, num_requests, H, max_context)
     part_m = part_l = part_acc = None
     if np_ > 1:
@@ -121,12 +123,12 @@ def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: tor
         check(lib().asb_latent_attention_mma(ptr(out), ptr(q_lat), ptr(pages), ptr(block_tables), ptr(req_q_start),
                                              ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H,
                                              rank, Dk - rank, pages.shape[2], block_tables.shape[1], ps, np_, float(scale),
-                                             stream()))  # fmt: skip
+                                             win, stream()))  # fmt: skip
     else:
         check(lib().asb_latent_attention(ptr(out), ptr(q_lat), ptr(pages), ptr(block_tables), ptr(req_q_start),
                                          ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), T, num_requests, H, rank,
                                          Dk - rank, pages.shape[2], block_tables.shape[1], ps, np_, float(scale),
-                                         dtype_code(pages), stream()))  # fmt: skip
+                                         win, dtype_code(pages), stream()))  # fmt: skip
     if np_ > 1:
         check(lib().asb_attention_reduce(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), T * H, np_, rank, FLOAT32, stream()))
     return out

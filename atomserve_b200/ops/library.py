@@ -60,7 +60,17 @@ _SIGNATURES = {
     "asb_lightning_scan": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "asb_recurrence_scan": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "asb_linear_recurrence": [_P, _P, _I, _I, _I, _I] + [_P] * 10 + [_I, _F, _F] + [_I] * 7 + [_P],
+    "asb_linear_recurrence_shared": [_P, _P, _I, _I, _I, _I] + [_P] * 10 + [_I, _F, _F] + [_I] * 8 + [_P],
     "asb_rotary_table": [_P, _P, _P, _I, _I, _P],
+    # a state-space recurrence's convolution, step sizes and gated norm
+    "asb_conv_steps": [_P, _P, _P, _P, _I, _I, _I] + [_P] * 7 + [_I] * 6 + [_P],
+    "asb_conv_state_update": [_P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
+    "asb_gate_group_norm": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    # blocks with a norm on a sublayer's input and on its output
+    "asb_add_normed": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _F, _F, _I, _P],
+    "asb_partial_add_normed": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _F, _F, _P],
+    "asb_bias_glu": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "asb_softcap": [_P, ctypes.c_longlong, _F, _P],
     # attention with a sink in the softmax's denominator
     "asb_paged_attention_sink": [_P] * 11 + [_I] * 10 + [_F, _I, _P],
     "asb_paged_attention_mma_sink": [_P] * 11 + [_I] * 10 + [_F, _I, _I, _I, _I, _P],
@@ -75,8 +85,8 @@ _SIGNATURES = {
     # attention over a cached latent
     "asb_latent_prepare": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "asb_head_matmul": [_P, _I, _I, _I, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "asb_latent_attention": [_P] * 9 + [_I] * 9 + [_F, _I, _P],
-    "asb_latent_attention_mma": [_P] * 9 + [_I] * 9 + [_F, _P],
+    "asb_latent_attention": [_P] * 9 + [_I] * 9 + [_F, _I, _I, _P],
+    "asb_latent_attention_mma": [_P] * 9 + [_I] * 9 + [_F, _I, _P],
     "asb_latent_attention_mma_supported": [_I, _I],
     "asb_head_matmul_mma": [_P, _I, _I, _I, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     # routed experts

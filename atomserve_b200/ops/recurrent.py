@@ -102,7 +102,8 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, st
                       token_gain: torch.Tensor | None = None, norm_state: torch.Tensor | None = None,
                       positions: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None, rotary_dim: int = 0,
                       q_scale: float = 1.0, k_scale: float = 1.0, activation: bool = False,
-                      segments: Segments | None = None, table: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
+                      segments: Segments | None = None, table: torch.Tensor | None = None,
+                      qk_share: int = 1) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
     """The general form of `lightning_attention`: S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t.
 
     a: `decay` float32 [H], or `token_decay` float32 [T, H]; b: `token_gain` float32 [T, H], or 1.
@@ -111,7 +112,9 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, st
     float32 [rotary_dim / 2]: q and k are rotated first, pairs (i, i + rotary_dim / 2) of each head's
     first rotary_dim entries by position * inv_freq[i] (`table`: the step's `rotary_table` of these
     positions and frequencies, where the caller has made it already). q_scale and k_scale multiply q
-    and k after that. Everything from the rotation on is float32. Returns (o float32 [T, H * V], n . q or None)."""
+    and k after that. `qk_share`: every group of this many neighbouring heads reads one q and one k
+    (proj then holds H / qk_share heads of D columns from q_off and from k_off); values, states and
+    outputs stay per head. Everything from the rotation on is float32. Returns (o float32 [T, H * V], n . q or None)."""
     require_cuda(proj, state, state_slots, req_q_start, decay, token_decay, token_gain, norm_state, positions, inv_freq)
     if proj.dim() != 2 or not proj.is_contiguous():
         raise KernelLibraryError("linear_recurrence: proj must be a contiguous [tokens, columns] tensor")
@@ -130,7 +133,9 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, st
             raise KernelLibraryError("linear_recurrence: index tensors must be contiguous int32")
     if positions is not None and (rotary_dim % 2 or rotary_dim > D or inv_freq is None or positions.shape[0] < T):
         raise KernelLibraryError(f"linear_recurrence: cannot rotate {rotary_dim} of {D} entries")
-    if max(q_off, k_off) + H * D > proj.shape[1] or v_off + H * V > proj.shape[1]:
+    if qk_share < 1 or H % qk_share or (qk_share > 1 and (norm_state is not None or positions is not None)):
+        raise KernelLibraryError(f"linear_recurrence: {H} heads sharing q and k in groups of {qk_share} (no normaliser, no rotation then)")
+    if max(q_off, k_off) + H // qk_share * D > proj.shape[1] or v_off + H * V > proj.shape[1]:
         raise KernelLibraryError("linear_recurrence: the column ranges lie outside proj")
     out = torch.empty(T, H * V, device=proj.device, dtype=torch.float32)
     nq = torch.empty(T, H, device=proj.device, dtype=torch.float32) if norm_state is not None else None
@@ -143,10 +148,11 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, st
     through = None  # with per-token decays: what is left of a state after each segment
 
     def run(state_, slots_, starts_, norm_state_, count, mode):
-        check(lib().asb_linear_recurrence(ptr(out), ptr(proj), proj.shape[1], q_off, k_off, v_off, ptr(state_), ptr(slots_),
-                                          ptr(starts_), ptr(decay), ptr(token_decay), ptr(token_gain), ptr(norm_state_),
-                                          ptr(nq), ptr(through), ptr(table) if rot else None, rot, float(q_scale), float(k_scale),
-                                          count, H, D, V, int(activation), mode, dtype_code(proj), stream()))  # fmt: skip
+        check(lib().asb_linear_recurrence_shared(ptr(out), ptr(proj), proj.shape[1], q_off, k_off, v_off, ptr(state_), ptr(slots_),
+                                                 ptr(starts_), ptr(decay), ptr(token_decay), ptr(token_gain), ptr(norm_state_),
+                                                 ptr(nq), ptr(through), ptr(table) if rot else None, rot, float(q_scale),
+                                                 float(k_scale), count, H, D, V, int(activation), mode, qk_share,
+                                                 dtype_code(proj), stream()))  # fmt: skip
 
     if segments is None:
         run(state, state_slots, req_q_start, norm_state, num_requests, 0)

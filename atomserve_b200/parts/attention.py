@@ -1,6 +1,13 @@
 """Grouped-query attention over cache pages, with optional per-head RMSNorm of q and k before
 the position encoding (Qwen3's form, atomserve/model.py:292-336), an optional sliding window,
-and no biases. Sizes, eps, the position encoding and the window are parameters."""
+and no biases. Sizes, eps, the position encoding, the score scale and the window are parameters;
+`names` gives the checkpoint's tensor names where they are not the `*_proj.weight` ones, and
+`value_dim` a value size that differs from the key size.
+
+Where value_dim != head_dim the pages and kernels run at the larger of the two: the narrower of
+(queries and keys) and (values) is padded with zero rows in the loaded weights, which changes no
+score and no output (the q/k norm's mean is taken over head_dim entries: the gains carry
+sqrt(head_dim / padded) and the kernel's eps is eps * head_dim / padded, the same quotient)."""
 
 from __future__ import annotations
 
@@ -23,11 +30,18 @@ class GQAttention(Mixer):
         position: PartSpec | None = None,
         window: int | None = None,
         scale: float | None = None,
+        value_dim: int | None = None,
+        names: dict[str, str] | None = None,
     ):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden_size, self.prefix = hidden_size, prefix
-        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        # key_dim and value_dim: the checkpoint's sizes; head_dim: what pages and kernels run at
+        self.key_dim, self.value_dim = head_dim, (head_dim if value_dim is None else value_dim)
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, max(self.key_dim, self.value_dim)
+        n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight", k_norm="k_norm.weight")
+        n.update(names or {})
+        self.names = {key: prefix + value for key, value in n.items()}
         self.qk_norm_eps = qk_norm_eps
         self.window = window
         self.scale = float(scale) if scale is not None else head_dim**-0.5
@@ -38,30 +52,59 @@ class GQAttention(Mixer):
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
     def tensor_specs(self) -> list[TensorSpec]:
-        p, d, hd = self.prefix, self.hidden_size, self.head_dim
+        n, d, kd, vd = self.names, self.hidden_size, self.key_dim, self.value_dim
         specs = [
-            TensorSpec(p + "q_proj.weight", (self.num_heads * hd, d)),
-            TensorSpec(p + "k_proj.weight", (self.num_kv_heads * hd, d)),
-            TensorSpec(p + "v_proj.weight", (self.num_kv_heads * hd, d)),
-            TensorSpec(p + "o_proj.weight", (d, self.num_heads * hd)),
+            TensorSpec(n["q"], (self.num_heads * kd, d)),
+            TensorSpec(n["k"], (self.num_kv_heads * kd, d)),
+            TensorSpec(n["v"], (self.num_kv_heads * vd, d)),
+            TensorSpec(n["o"], (d, self.num_heads * vd)),
         ]
         if self.qk_norm_eps is not None:
             specs += [
-                TensorSpec(p + "q_norm.weight", (hd,), kind="gain", init="gain"),
-                TensorSpec(p + "k_norm.weight", (hd,), kind="gain", init="gain"),
+                TensorSpec(n["q_norm"], (kd,), kind="gain", init="gain"),
+                TensorSpec(n["k_norm"], (kd,), kind="gain", init="gain"),
             ]
         return specs
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
-        p = self.prefix
+        n, hd, kd, vd = self.names, self.head_dim, self.key_dim, self.value_dim
+
+        def rows_per_head(w: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+            if size == hd:
+                return w
+            padded = w.new_zeros(heads, hd, w.shape[1])
+            padded[:, :size] = w.view(heads, size, w.shape[1])
+            return padded.view(heads * hd, w.shape[1])
+
         # q, k and v stacked along the output rows: one product instead of three
         # (atomserve/loader.py:112-116)
-        self.qkv_proj = torch.cat([tensors[p + f"{n}_proj.weight"] for n in "qkv"]).contiguous()
-        self.o_proj = tensors[p + "o_proj.weight"]
+        self.qkv_proj = torch.cat([rows_per_head(tensors[n["q"]], self.num_heads, kd),
+                                   rows_per_head(tensors[n["k"]], self.num_kv_heads, kd),
+                                   rows_per_head(tensors[n["v"]], self.num_kv_heads, vd)]).contiguous()  # fmt: skip
+        self.o_proj = tensors[n["o"]]
+        if vd != hd:  # the padded value entries are zero: their columns of the output projection too
+            o = self.o_proj.new_zeros(self.o_proj.shape[0], self.num_heads, hd)
+            o[:, :, :vd] = self.o_proj.view(-1, self.num_heads, vd)
+            self.o_proj = o.view(-1, self.num_heads * hd).contiguous()
+        self.kernel_eps = self.qk_norm_eps
         if self.qk_norm_eps is not None:
-            self.q_gain, self.k_gain = tensors[p + "q_norm.weight"], tensors[p + "k_norm.weight"]
+            self.q_gain, self.k_gain = tensors[n["q_norm"]], tensors[n["k_norm"]]
+            if kd != hd:
+                pad = (kd / hd) ** 0.5
+                self.q_gain = torch.cat([self.q_gain * pad, self.q_gain.new_zeros(hd - kd)]).contiguous()
+                self.k_gain = torch.cat([self.k_gain * pad, self.k_gain.new_zeros(hd - kd)]).contiguous()
+                self.kernel_eps = self.qk_norm_eps * kd / hd
         if self.position is not None:
             self.position.prepare(self.o_proj.device)
+            rotary = self.position.fused_rotary()
+            if rotary is not None and rotary.magnitude != 1.0:
+                # cosines and sines times a constant: the turned entries of q and k times it, which
+                # the gains of the norm before the rotation carry (a pair's two entries both turn)
+                if self.qk_norm_eps is None:
+                    raise NotImplementedError("a rotation with a magnitude needs the q/k norm, whose gains carry it")
+                scale = torch.ones_like(self.q_gain)
+                scale[: rotary.rotary_dim] = rotary.magnitude
+                self.q_gain, self.k_gain = (self.q_gain * scale).contiguous(), (self.k_gain * scale).contiguous()
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext,
                 cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
@@ -73,6 +116,11 @@ class GQAttention(Mixer):
         if after_linear is None:
             return super().forward_then(h, residual, ctx, cache, write_cache, then)
         return after_linear(self.attend(h, ctx, cache, write_cache), self.o_proj, residual)
+
+    def forward_for_stream(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool = True):
+        """mix(h) for a block that adds it to a float32 stream itself: float32, or the output
+        projection's partial sums for the norm that follows to add up (`ops.linear_for_stream`)."""
+        return ops.linear_for_stream(self.attend(h, ctx, cache, write_cache), self.o_proj)
 
     def attend(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None, write_cache: bool) -> torch.Tensor:
         """The heads' outputs side by side, [T, H * hd], before the output projection."""
@@ -95,7 +143,7 @@ class GQAttention(Mixer):
                 qkv = ops.linear(h, weight)
             q = ops.qk_norm_rope_store(
                 qkv, H, kv_heads, hd, ctx.positions,
-                q_gain=self.q_gain, k_gain=self.k_gain, eps=self.qk_norm_eps or 0.0,
+                q_gain=self.q_gain, k_gain=self.k_gain, eps=self.kernel_eps or 0.0,
                 inv_freq=rotary.inv_freq if rotary else None, rotary_dim=rotary.rotary_dim if rotary else 0,
                 slots=cache.slots if write_cache else None,
                 k_cache=cache.k if write_cache else None, v_cache=cache.v if write_cache else None,
@@ -119,8 +167,8 @@ class GQAttention(Mixer):
         normed = qkv
         if self.qk_norm_eps is not None:
             heads = qkv.view(T, H + 2 * kv_heads, hd)
-            q = ops.rms_norm(heads[:, :H].reshape(T * H, hd), self.q_gain, self.qk_norm_eps).view(T, H, hd)
-            k = ops.rms_norm(heads[:, H : H + kv_heads].reshape(T * kv_heads, hd), self.k_gain, self.qk_norm_eps).view(T, kv_heads, hd) if kv_heads else None
+            q = ops.rms_norm(heads[:, :H].reshape(T * H, hd), self.q_gain, self.kernel_eps).view(T, H, hd)
+            k = ops.rms_norm(heads[:, H : H + kv_heads].reshape(T * kv_heads, hd), self.k_gain, self.kernel_eps).view(T, kv_heads, hd) if kv_heads else None
         else:
             heads = qkv.view(T, H + 2 * kv_heads, hd)
             q, k = heads[:, :H].contiguous(), (heads[:, H : H + kv_heads].contiguous() if kv_heads else None)

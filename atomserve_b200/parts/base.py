@@ -157,11 +157,13 @@ class FusedRotary:
     """An encoding that a mixer's fused kernel can apply by itself: each head's first
     `rotary_dim` dimensions are turned, pair i by the angle position * inv_freq[i] (`inv_freq`:
     float32 [rotary_dim / 2] on the device). `pairing` says which entries make pair i: "half",
-    (i, i + rotary_dim / 2), or "interleaved", (2i, 2i + 1)."""
+    (i, i + rotary_dim / 2), or "interleaved", (2i, 2i + 1). `magnitude` multiplies every cosine and
+    sine (encodings that stretch their frequencies for long contexts scale the turned entries)."""
 
     inv_freq: torch.Tensor
     rotary_dim: int
     pairing: str = "half"
+    magnitude: float = 1.0
 
 
 class PositionEncoding(Part):
@@ -299,5 +301,5 @@ def _ensure_builtin() -> None:
     if "rms_norm" not in _REGISTRIES["norm"]:
         from atomserve_b200.parts import (  # noqa: F401
             attention, block, embedding, experts, latent_attention, lightning, matrix_memory, mlp, norms, parallel, rotary,
-            sink_attention, token_input,
+            sink_attention, state_space, token_input,
         )

@@ -106,6 +106,29 @@ class OutputNormBlock(PostNormBlock):
         return x, h
 
 
+class SandwichNormBlock(PostNormBlock):
+    """The arrangement with a norm on each sublayer's input and on its output, over a float32
+    residual stream: x <- x + N1b(mixer(N1(x))); x <- x + N2b(ff(N2(x))). The norms are
+    `SandwichNorm`s (two gains each). A layer without a feed-forward ends after its first half. The
+    kernel that adds a sublayer's normed output also norms the sum for whatever reads it next (the
+    feed-forward, or the next block's mixer), so the normed input travels from block to block in
+    the place where pre-norm blocks hand it on. Sublayers give their last product as float32 or as
+    partial sums (`forward_for_stream`); a feed-forward's `output_bias` joins it before the norm."""
+
+    def forward_chain(self, x: torch.Tensor, normed: torch.Tensor | None, ctx: StepContext, cache: CacheView | None,
+                      write_cache: bool, then: Norm | None) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
+        h = normed if normed is not None else self.mixer_norm.forward(x)
+        mix = getattr(self.mixer, "forward_for_stream", None)
+        y = mix(h, ctx, cache, write_cache) if mix is not None else self.mixer.forward(h, None, ctx, cache, write_cache)
+        if not self.has_feed_forward:
+            return self.mixer_norm.add_forward(x, y, then)
+        x, h = self.mixer_norm.add_forward(x, y, self.feed_forward_norm)
+        ff = getattr(self.feed_forward, "forward_for_stream", None)
+        y = ff(h, ctx) if ff is not None else self.feed_forward.forward(h, None, ctx)
+        return self.feed_forward_norm.add_forward(x, y, then, getattr(self.feed_forward, "output_bias", None))
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "output_norm", OutputNormBlock)
 register_part("block", "post_norm", PostNormBlock)

@@ -42,9 +42,35 @@ class ScaledEmbedding(TokenEmbedding):
         return ops.embedding_scaled(token_ids, self.table, self.scale, self.status)
 
 
+class NormedEmbedding(TokenEmbedding):
+    """RMS norm of table[token] with a gain (`norm_tensor`), as float32: the start of a residual
+    stream that is kept in float32 whatever the compute dtype."""
+
+    def __init__(self, hidden_size: int, prefix: str, vocab_size: int, eps: float, tensor: str | None = None,
+                 norm_tensor: str | None = None):  # fmt: skip
+        super().__init__(hidden_size, prefix, vocab_size, tensor)
+        self.eps, self.norm_name = float(eps), norm_tensor or prefix + "norm"
+        self.gain: torch.Tensor | None = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return super().tensor_specs() + [TensorSpec(self.norm_name, (self.hidden_size,), kind="gain", init="gain")]
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        super().load(tensors)
+        self.gain = tensors[self.norm_name]
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        rows = ops.embedding_scaled(token_ids, self.table, 1.0, self.status)
+        return ops.scaled_add_rms_norm(rows, None, 1.0, self.gain, self.eps, torch.float32)[0]
+
+
 class LMHead(Part):
-    def __init__(self, hidden_size: int, prefix: str, vocab_size: int, tied: bool, tensor: str | None = None):
+    """`softcap`: logits <- softcap tanh(logits / softcap), on the float32 logits."""
+
+    def __init__(self, hidden_size: int, prefix: str, vocab_size: int, tied: bool, tensor: str | None = None,
+                 softcap: float | None = None):  # fmt: skip
         self.hidden_size, self.vocab_size, self.tied, self.name = hidden_size, vocab_size, tied, tensor or prefix + "weight"
+        self.softcap = float(softcap) if softcap else None
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -58,9 +84,11 @@ class LMHead(Part):
         self.weight = embedding.table
 
     def forward(self, hidden: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        return ops.linear(hidden, self.weight, out_dtype=torch.float32, out=out)
+        logits = ops.linear(hidden, self.weight, out_dtype=torch.float32, out=out)
+        return ops.softcap_(logits, self.softcap) if self.softcap else logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "scaled_embedding", ScaledEmbedding)
+register_part("embedding", "normed_embedding", NormedEmbedding)
 register_part("head", "lm_head", LMHead)

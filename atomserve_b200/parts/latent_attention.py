@@ -8,6 +8,10 @@ on the query side (scores against c itself, the weighted sum of c up-projected a
 the pages are read as they are. A sigmoid gate per head, projected from the same input,
 multiplies the head's output before the output projection.
 
+`rot_dim=0` with no position encoding is the form without a position-encoded part; `gated=False`
+the form without the gate; with `window` a query sees its last `window` positions only (itself
+included) and pages the window has passed are given back.
+
 A mixer built with `reads_cache_of_another=True` has no down-projection: the run order gives
 it the pages of an earlier latent-attention entry (`LayerCall.cache_from`), which it reads with
 its own queries and up-projections.
@@ -26,17 +30,21 @@ PAGE = "latent"
 
 class LatentAttention(Mixer):
     def __init__(self, hidden_size: int, prefix: str, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
-                 scale: float, eps: float, position: PartSpec, reads_cache_of_another: bool = False):  # fmt: skip
+                 scale: float, eps: float, position: PartSpec | None = None, reads_cache_of_another: bool = False,
+                 gated: bool = True, window: int | None = None):  # fmt: skip
+        if (rot_dim > 0) != (position is not None):
+            raise ValueError("a position-encoded key part needs a position encoding, and the other way round")
         self.hidden_size, self.prefix = hidden_size, prefix
         self.heads, self.dim, self.rot_dim, self.vdim, self.kv_rank = heads, dim, rot_dim, vdim, kv_rank
         self.scale, self.eps, self.reads_only = float(scale), float(eps), reads_cache_of_another
-        self.position = build_part("position", position, hidden_size)
+        self.gated, self.window = gated, window
+        self.position = build_part("position", position, hidden_size) if position is not None else None
         self.in_proj = self.uk = self.uv_t = self.o_proj = self.latent_gain = None
 
     def cache_spec(self) -> PageSpec | None:
         if self.reads_only:
             return None
-        return PageSpec((PageTensor(PAGE, 1, self.kv_rank + self.rot_dim),))
+        return PageSpec((PageTensor(PAGE, 1, self.kv_rank + self.rot_dim),), self.window)
 
     def tensor_specs(self) -> list[TensorSpec]:
         p, d, H = self.prefix, self.hidden_size, self.heads
@@ -44,9 +52,8 @@ class LatentAttention(Mixer):
             TensorSpec(p + "q", (H * (self.dim + self.rot_dim), d)),
             TensorSpec(p + "uk", (H * self.dim, self.kv_rank)),
             TensorSpec(p + "uv", (H * self.vdim, self.kv_rank)),
-            TensorSpec(p + "g", (H, d)),
             TensorSpec(p + "o", (d, H * self.vdim)),
-        ]
+        ] + ([TensorSpec(p + "g", (H, d))] if self.gated else [])
         if not self.reads_only:
             specs += [
                 TensorSpec(p + "dkv", (self.kv_rank + self.rot_dim, d)),
@@ -57,7 +64,7 @@ class LatentAttention(Mixer):
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         p, H = self.prefix, self.heads
         # queries, (down-projection,) gates stacked along the output rows: one product
-        rows = [tensors[p + "q"]] + ([] if self.reads_only else [tensors[p + "dkv"]]) + [tensors[p + "g"]]
+        rows = [tensors[p + "q"]] + ([] if self.reads_only else [tensors[p + "dkv"]]) + ([tensors[p + "g"]] if self.gated else [])
         self.in_proj = torch.cat(rows).contiguous()
         # per head, keys' up-projection [dim, rank] (absorbed into the queries) and values' [rank, vdim];
         # the tensor-core kernel takes each with its inner size last instead
@@ -68,11 +75,13 @@ class LatentAttention(Mixer):
         self.uv_t = (uv if self.uv_nk else uv.transpose(1, 2)).contiguous()
         self.o_proj = tensors[p + "o"]
         self.latent_gain = None if self.reads_only else tensors[p + "dkv.norm"]
-        self.position.prepare(self.o_proj.device)
-        rotary = self.position.fused_rotary()
-        if rotary is None or rotary.pairing != "interleaved" or rotary.rotary_dim > self.rot_dim:
-            raise ValueError("latent attention turns neighbouring pairs of its position-encoded part by position x frequency")
-        self.rotary = rotary
+        self.rotary = None
+        if self.position is not None:
+            self.position.prepare(self.o_proj.device)
+            rotary = self.position.fused_rotary()
+            if rotary is None or rotary.pairing != "interleaved" or rotary.rotary_dim > self.rot_dim or rotary.magnitude != 1.0:
+                raise ValueError("latent attention turns neighbouring pairs of its position-encoded part by position x frequency")
+            self.rotary = rotary
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext,
                 cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
@@ -97,12 +106,15 @@ class LatentAttention(Mixer):
         q_lat = torch.empty(T, H, R + Rt, device=h.device, dtype=torch.float32)
         ops.head_matmul(proj[:, :q_cols].view(T, H, D + Rt)[:, :, :D], self.uk, q_lat[:, :, :R], w_is_nk=self.uk_nk)
         ops.latent_prepare(proj, 0, None if self.reads_only else q_cols, q_lat, None if self.reads_only else pages,
-                           self.latent_gain, self.rotary.inv_freq, ctx.positions, None if self.reads_only else cache.slots,
-                           heads=H, dim=D, rank=R, rot=Rt, rot_dims=self.rotary.rotary_dim, eps=self.eps)  # fmt: skip
+                           self.latent_gain, self.rotary.inv_freq if self.rotary else None, ctx.positions,
+                           None if self.reads_only else cache.slots, heads=H, dim=D, rank=R, rot=Rt,
+                           rot_dims=self.rotary.rotary_dim if self.rotary else 0, eps=self.eps)  # fmt: skip
         mixed = ops.latent_attention(q_lat, pages, cache.block_tables, ctx.req_q_start, ctx.req_pos_start, rank=R,
-                                     num_requests=ctx.num_requests, max_context=ctx.max_context, scale=self.scale)  # fmt: skip
+                                     num_requests=ctx.num_requests, max_context=ctx.max_context, scale=self.scale,
+                                     window=self.window)  # fmt: skip
         out = torch.empty(T, H * V, device=h.device, dtype=h.dtype)
-        ops.head_matmul(mixed, self.uv_t, out.view(T, H, V), gate=proj[:, gate_off : gate_off + H], w_is_nk=self.uv_nk)
+        ops.head_matmul(mixed, self.uv_t, out.view(T, H, V), gate=proj[:, gate_off : gate_off + H] if self.gated else None,
+                        w_is_nk=self.uv_nk)  # fmt: skip
         return out
 
 

@@ -59,7 +59,7 @@ class LightningAttention(Mixer):
         if self.position is not None:
             self.position.prepare(self.o_proj.device)
             rotary = self.position.fused_rotary()
-            if rotary is None or rotary.pairing != "half":
+            if rotary is None or rotary.pairing != "half" or rotary.magnitude != 1.0:
                 raise NotImplementedError("the recurrence's kernel turns pairs (i, i + rotary_dim / 2) by position x frequency only")
 
     def input_weights(self) -> torch.Tensor:

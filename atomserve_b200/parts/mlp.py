@@ -52,4 +52,48 @@ class SwiGLU(FeedForward):
         return after_linear(self.hidden(h), self.down_proj, residual)
 
 
+class GatedMLP(FeedForward):
+    """down(act(gate h + b_gate) * (up h + b_up)) + b_down with act "silu", "gelu_tanh" or "gelu" and
+    optional biases; tensors `gate`, `up`, `down` and their `.b`. The down projection's bias is
+    `output_bias`: a block that norms the sublayer's output adds it in that norm's kernel."""
+
+    def __init__(self, hidden_size: int, prefix: str, intermediate_size: int, activation: str = "gelu_tanh", biases: bool = True):
+        if activation not in ops.sandwich.GLU_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {sorted(ops.sandwich.GLU_ACTIVATIONS)}")
+        self.hidden_size, self.prefix, self.intermediate_size = hidden_size, prefix, intermediate_size
+        self.activation, self.biases = activation, biases
+        self.gate_up = self.down = self.gate_up_bias = self.output_bias = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        p, d, i = self.prefix, self.hidden_size, self.intermediate_size
+        specs = [TensorSpec(p + "gate", (i, d)), TensorSpec(p + "up", (i, d)), TensorSpec(p + "down", (d, i))]
+        if self.biases:
+            specs += [TensorSpec(p + "gate.b", (i,), kind="gain", init="normal"), TensorSpec(p + "up.b", (i,), kind="gain", init="normal"),
+                      TensorSpec(p + "down.b", (d,), kind="gain", init="normal")]  # fmt: skip
+        return specs
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        p = self.prefix
+        self.gate_up = torch.cat([tensors[p + "gate"], tensors[p + "up"]]).contiguous()  # one product for both
+        self.down = tensors[p + "down"]
+        if self.biases:
+            self.gate_up_bias = torch.cat([tensors[p + "gate.b"], tensors[p + "up.b"]]).contiguous()
+            self.output_bias = tensors[p + "down.b"]
+
+    def inner(self, h: torch.Tensor) -> torch.Tensor:
+        return ops.bias_glu(ops.linear(h, self.gate_up), self.gate_up_bias, self.activation)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext) -> torch.Tensor:
+        out = ops.linear(self.inner(h), self.down, None, out_dtype=torch.float32)
+        if self.output_bias is not None:
+            out += self.output_bias
+        return out if residual is None else residual + out.to(residual.dtype)
+
+    def forward_for_stream(self, h: torch.Tensor, ctx: StepContext):
+        """ff(h) without the output bias, for a block that adds it to a float32 stream itself:
+        float32, or the down projection's partial sums (`ops.linear_for_stream`)."""
+        return ops.linear_for_stream(self.inner(h), self.down)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "gated_mlp", GatedMLP)

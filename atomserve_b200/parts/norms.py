@@ -98,6 +98,41 @@ class OutputNorm(Norm):
                                      centred=self.centred, halves=halves)  # fmt: skip
 
 
+class SandwichNorm(Norm):
+    """The two norms around one sublayer of a block that norms a sublayer's input and its output
+    over a float32 stream, x <- x + N_out(f(N_in(x))), both RMS norms with a gain: `forward` is
+    N_in of (rows of) the stream in the compute dtype; `add_forward(x, y, then, bias)` is the new
+    stream x + N_out(y + bias) and, where `then` (the norm whose input comes next) is given, that
+    norm's N_in of it in the compute dtype, from one kernel. `tensor` and `out_tensor` name the
+    two gains."""
+
+    def __init__(self, hidden_size: int, prefix: str, eps: float, tensor: str | None = None, out_tensor: str | None = None):
+        self.width, self.eps = hidden_size, float(eps)
+        self.name, self.out_name = tensor or prefix + "weight", out_tensor or prefix + "out.weight"
+        self.gain = self.out_gain = None
+        self.dtype = torch.float32
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.width,), kind="gain", init="gain"),
+                TensorSpec(self.out_name, (self.width,), kind="gain", init="gain")]  # fmt: skip
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.gain, self.out_gain = tensors[self.name], tensors[self.out_name]
+
+    def bind_dtype(self, dtype: torch.dtype) -> None:
+        self.dtype = dtype
+
+    def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        return ops.scaled_add_rms_norm(x, None, 1.0, self.gain, self.eps, self.dtype, rows, want_stream=False)[1]
+
+    def add_forward(self, x: torch.Tensor, y, then: Norm | None = None, bias: torch.Tensor | None = None):
+        gain_next = getattr(then, "gain", None) if then is not None else None
+        if then is not None and (gain_next is None or not hasattr(then, "eps")):
+            stream, _ = ops.add_normed(x, y, self.out_gain, self.eps, None, 0.0, self.dtype, bias)
+            return stream, then.forward(stream)
+        return ops.add_normed(x, y, self.out_gain, self.eps, gain_next, then.eps if then is not None else 0.0, self.dtype, bias)
+
+
 class NoNorm(Norm):
     """The norm of a sublayer that a layer does not have."""
 
@@ -111,4 +146,5 @@ class NoNorm(Norm):
 register_part("norm", "rms_norm", RMSNorm)
 register_part("norm", "stream_rms_norm", StreamRMSNorm)
 register_part("norm", "output_norm", OutputNorm)
+register_part("norm", "sandwich_norm", SandwichNorm)
 register_part("norm", "none", NoNorm)

@@ -6,6 +6,8 @@ mixers whose fused kernels know that pairing apply it (latent attention)."""
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from atomserve_b200 import ops
@@ -39,4 +41,43 @@ class Rotary(PositionEncoding):
         return ops.rotary(x, positions, self.inv_freq, self.rotary_dim)
 
 
+class ScaledRotary(Rotary):
+    """Rotary encoding whose frequencies are stretched for contexts longer than the `original` one
+    (the scheme known as YaRN). With f_i = theta^(-2i / rotary_dim): index(t) = rotary_dim
+    ln(original / (2 pi t)) / (2 ln theta) is where a frequency makes t turns over the original
+    context; lo = max(floor(index(fast)), 0), hi = min(ceil(index(slow)), rotary_dim - 1),
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1); the frequency becomes
+    f_i / factor * ramp_i + f_i (1 - ramp_i), and cosines and sines are multiplied by
+    0.1 ln(factor) + 1 (`FusedRotary.magnitude`)."""
+
+    def __init__(self, hidden_size: int, prefix: str, head_dim: int, theta: float, factor: float, original: float,
+                 fast: float, slow: float, rotary_dim: int | None = None, pairing: str = "half"):  # fmt: skip
+        super().__init__(hidden_size, prefix, head_dim, theta, rotary_dim, pairing)
+        if not factor >= 1.0 or not original > 0 or not fast > 0 or not slow > 0:
+            raise ValueError("a scaled rotary encoding needs factor >= 1 and positive original, fast and slow")
+        self.factor, self.original, self.fast, self.slow = float(factor), float(original), float(fast), float(slow)
+        self.magnitude = 0.1 * math.log(self.factor) + 1.0
+
+    def prepare(self, device: torch.device) -> None:
+        dims = self.rotary_dim
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = self.theta ** (-2.0 * i / dims) if dims else i
+
+        def index(turns: float) -> float:
+            return dims * math.log(self.original / (2 * math.pi * turns)) / (2 * math.log(self.theta))
+
+        if dims:
+            lo, hi = max(math.floor(index(self.fast)), 0), min(math.ceil(index(self.slow)), dims - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / self.factor * ramp + f * (1.0 - ramp)
+        self.inv_freq = f.to(torch.float32).to(device)
+
+    def fused_rotary(self) -> FusedRotary:
+        return FusedRotary(self.inv_freq, self.rotary_dim, self.pairing, self.magnitude)
+
+    def apply(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError("the stand-alone rotary kernel has no magnitude; mixers apply this encoding fused")
+
+
 register_part("position", "rotary", Rotary)
+register_part("position", "scaled_rotary", ScaledRotary)
