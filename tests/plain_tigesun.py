@@ -1,8 +1,13 @@
 """A plain, slow implementation of the Tigesun design for the tests: one function per mechanism,
 float64 on the CPU, whole sequences at once, no cache, no batching. It shares no code with the package.
 
-A model is (config dict, tensors dict name -> float64 tensor). Tensor names: `embed`, `embed.norm`,
+A model is (config dict, tensors dict name -> tensor). Tensor names: `embed`, `embed.norm`,
 `l<i>.norm1`, `l<i>.norm1b`, `l<i>.norm2`, `l<i>.norm2b`, `l<i>.mix.*`, `l<i>.mlp.*`, `final.norm`.
+
+`stored` (identity by default) is applied to everything that an engine may keep in 16 bits:
+projections, convolution outputs, attention outputs, gated heads, a sublayer's normed input. With
+`stored = lambda t: t.bfloat16().double()` the implementation shows what rounding alone does to a
+model's logits; the tests measure the engine's bfloat16 error against that.
 """
 
 from __future__ import annotations
@@ -76,36 +81,38 @@ def masked_softmax_attention(q, k, v, scale: float, window: int | None) -> torch
     return torch.einsum("hij,jhv->ihv", torch.softmax(scores, dim=-1), v)
 
 
-def attention_mixer(h, w: dict, m: dict, eps: float) -> torch.Tensor:
+def attention_mixer(h, w: dict, m: dict, eps: float, stored=lambda t: t) -> torch.Tensor:
     """Grouped-query attention: per-head RMS norm of q and k with one gain for all heads, then the
     rotation, scores times `scale`, causal softmax, output projection."""
     T = h.shape[0]
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w["q"].T).view(T, H, D)
-    k = (h @ w["k"].T).view(T, G, D)
-    v = (h @ w["v"].T).view(T, G, V)
+    q = stored(h @ w["q"].T).view(T, H, D)
+    k = stored(h @ w["k"].T).view(T, G, D)
+    v = stored(h @ w["v"].T).view(T, G, V)
     q, k = rms(q, w["q.norm"], eps), rms(k, w["k.norm"], eps)
     rot = m.get("rot")
     if rot and rot["dims"]:
         cos, sin = scaled_rotary_tables(torch.arange(T), rot)
         q, k = rotate_half(q, cos, sin, rot["dims"]), rotate_half(k, cos, sin, rot["dims"])
+    q, k = stored(q), stored(k)
     k = k.repeat_interleave(H // G, dim=1)
     v = v.repeat_interleave(H // G, dim=1)
-    o = masked_softmax_attention(q, k, v, m["scale"], None)
+    window = m["mask"]["size"] if m.get("mask") else None
+    o = stored(masked_softmax_attention(q, k, v, m["scale"], window))
     return o.reshape(T, H * V) @ w["o"].T
 
 
-def latent_attention_mixer(h, w: dict, m: dict, eps: float) -> torch.Tensor:
+def latent_attention_mixer(h, w: dict, m: dict, eps: float, stored=lambda t: t) -> torch.Tensor:
     """Attention whose keys and values are up-projections of one normed latent per token, without
     positions, in a sliding window."""
     T = h.shape[0]
     H, D, V = m["heads"], m["dim"], m["vdim"]
-    q = (h @ w["q"].T).view(T, H, D)
-    c = rms(h @ w["dkv"].T, w["dkv.norm"], eps)
+    q = stored(h @ w["q"].T).view(T, H, D)
+    c = stored(rms(stored(h @ w["dkv"].T), w["dkv.norm"], eps))
     k = (c @ w["uk"].T).view(T, H, D)
     v = (c @ w["uv"].T).view(T, H, V)
     window = m["mask"]["size"] if m.get("mask") else None
-    o = masked_softmax_attention(q, k, v, m["scale"], window)
+    o = stored(masked_softmax_attention(q, k, v, m["scale"], window))
     return o.reshape(T, H * V) @ w["o"].T
 
 
@@ -121,14 +128,14 @@ def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor) -> torc
     return out
 
 
-def mamba2_mixer(h, w: dict, m: dict, eps: float) -> torch.Tensor:
+def mamba2_mixer(h, w: dict, m: dict, eps: float, stored=lambda t: t) -> torch.Tensor:
     """A selective state-space layer with a scalar decay per head, token by token."""
     T = h.shape[0]
     H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
     inner = H * P
-    proj = h @ w["in"].T
+    proj = stored(h @ w["in"].T)
     z, xbc, dt = proj[:, :inner], proj[:, inner : 2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N :]
-    xbc = silu(causal_conv(xbc, w["conv"], w["conv.b"]))
+    xbc = stored(silu(causal_conv(xbc, w["conv"], w["conv.b"])))
     x = xbc[:, :inner].view(T, H, P)
     B = xbc[:, inner : inner + G * N].view(T, G, N).repeat_interleave(H // G, dim=1)
     C = xbc[:, inner + G * N :].view(T, G, N).repeat_interleave(H // G, dim=1)
@@ -141,12 +148,13 @@ def mamba2_mixer(h, w: dict, m: dict, eps: float) -> torch.Tensor:
         y[t] = torch.einsum("hnp,hn->hp", S, C[t]) + w["D"][:, None] * x[t]
     y = y.reshape(T, inner) * silu(z)
     parts = m["norm_groups"]
-    y = rms(y.view(T, parts, inner // parts), None, eps).reshape(T, inner) * w["norm"]
+    y = stored(rms(y.view(T, parts, inner // parts), None, eps).reshape(T, inner) * w["norm"])
     return y @ w["o"].T
 
 
-def gated_mlp(h, w: dict) -> torch.Tensor:
-    return (gelu_tanh(h @ w["gate"].T + w["gate.b"]) * (h @ w["up"].T + w["up.b"])) @ w["down"].T + w["down.b"]
+def gated_mlp(h, w: dict, stored=lambda t: t) -> torch.Tensor:
+    inner = stored(gelu_tanh(stored(h @ w["gate"].T) + w["gate.b"]) * (stored(h @ w["up"].T) + w["up.b"]))
+    return inner @ w["down"].T + w["down.b"]
 
 
 MIXERS = {"attention": attention_mixer, "latent_attention": latent_attention_mixer, "mamba2": mamba2_mixer}
@@ -156,20 +164,84 @@ def sub(tensors: dict, prefix: str) -> dict:
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(config: dict, tensors: dict, tokens: list[int], return_layers: bool = False):
+def forward(config: dict, tensors: dict, tokens: list[int], return_layers: bool = False, stored=lambda t: t):
     """Logits [T, vocab] of one sequence (and the stream after every layer)."""
     eps = config["norm"]["eps"]
+    tensors = {k: v.double() for k, v in tensors.items()}
     x = rms(tensors["embed"][torch.tensor(tokens)], tensors["embed.norm"], eps)
     after = []
     for i, layer in enumerate(config["layers"]):
         p = f"l{layer.get('weights_of', i)}."
-        mix = MIXERS[layer["type"]](rms(x, tensors[p + "norm1"], eps), sub(tensors, p + "mix."), layer["mixer"], eps)
+        mix = MIXERS[layer["type"]](stored(rms(x, tensors[p + "norm1"], eps)), sub(tensors, p + "mix."), layer["mixer"], eps, stored)
         x = x + rms(mix, tensors[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            x = x + rms(gated_mlp(rms(x, tensors[p + "norm2"], eps), sub(tensors, p + "mlp.")), tensors[p + "norm2b"], eps)
+            ff = gated_mlp(stored(rms(x, tensors[p + "norm2"], eps)), sub(tensors, p + "mlp."), stored)
+            x = x + rms(ff, tensors[p + "norm2b"], eps)
         after.append(x)
-    logits = rms(x, tensors["final.norm"], eps) @ tensors["embed"].T
+    logits = stored(rms(x, tensors["final.norm"], eps)) @ tensors["embed"].T
     cap = config.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def tensor_shapes(config: dict) -> dict[str, tuple]:
+    """Name -> shape of every tensor of a model with this configuration."""
+    d = config["width"]
+    shapes = {"embed": (config["vocab"], d), "embed.norm": (d,), "final.norm": (d,)}
+    for i, layer in enumerate(config["layers"]):
+        if "weights_of" in layer:
+            continue
+        p, m = f"l{i}.", layer["mixer"]
+        shapes[p + "norm1"] = shapes[p + "norm1b"] = (d,)
+        if layer["type"] == "attention":
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            shapes.update({p + "mix.q": (H * D, d), p + "mix.k": (G * D, d), p + "mix.v": (G * V, d), p + "mix.q.norm": (D,),
+                           p + "mix.k.norm": (D,), p + "mix.o": (d, H * V)})  # fmt: skip
+        elif layer["type"] == "latent_attention":
+            H, D, V, r = m["heads"], m["dim"], m["vdim"], m["kv_rank"]
+            shapes.update({p + "mix.q": (H * D, d), p + "mix.dkv": (r, d), p + "mix.dkv.norm": (r,), p + "mix.uk": (H * D, r),
+                           p + "mix.uv": (H * V, r), p + "mix.o": (d, H * V)})  # fmt: skip
+        else:
+            H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            inner, channels = H * P, H * P + 2 * G * N
+            shapes.update({p + "mix.in": (2 * inner + 2 * G * N + H, d), p + "mix.conv": (channels, m["conv"]), p + "mix.conv.b": (channels,),
+                           p + "mix.dt_bias": (H,), p + "mix.A_log": (H,), p + "mix.D": (H,), p + "mix.norm": (inner,),
+                           p + "mix.o": (d, inner)})  # fmt: skip
+        if layer.get("mlp") is not None:
+            f = layer["mlp"]["ff"]
+            shapes[p + "norm2"] = shapes[p + "norm2b"] = (d,)
+            shapes.update({p + "mlp.gate": (f, d), p + "mlp.gate.b": (f,), p + "mlp.up": (f, d), p + "mlp.up.b": (f,),
+                           p + "mlp.down": (d, f), p + "mlp.down.b": (d,)})  # fmt: skip
+    return shapes
+
+
+def random_checkpoint(config: dict, seed: int) -> dict[str, torch.Tensor]:
+    """Random float32 weights whose matrices are exact in bfloat16: matrices N(0, 1 / fan_in) (the
+    embedding N(0, 1), convolution taps N(0, 1 / taps)), gains 1 + N(0, 0.1), biases N(0, 0.3),
+    step biases spread over (-3, 1) and decay rates over exp(-1.5 .. 1.5), so that some heads forget
+    within a few tokens and others keep hundreds."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in tensor_shapes(config).items():
+        if name.endswith("dt_bias"):
+            w[name] = torch.linspace(-3.0, 1.0, shape[0])[torch.randperm(shape[0], generator=g)]
+        elif name.endswith("A_log"):
+            w[name] = torch.linspace(-1.5, 1.5, shape[0])[torch.randperm(shape[0], generator=g)]
+        elif name.endswith(".b"):
+            w[name] = 0.3 * torch.randn(shape, generator=g)
+        elif len(shape) == 1:
+            w[name] = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        else:
+            std = 1.0 if name == "embed" else shape[1] ** -0.5
+            w[name] = (torch.randn(shape, generator=g) * std).bfloat16().float()
+    return w
+
+
+def greedy_generate(config: dict, tensors: dict, prompt: list[int], n: int) -> list[int]:
+    """The n tokens that follow `prompt` when the largest logit is taken each time (the whole
+    sequence is run again for every token: slow and stateless)."""
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(forward(config, tensors, tokens)[-1].argmax()))
+    return tokens[len(prompt) :]
