@@ -52,8 +52,14 @@ class TigesunConfig:
         return config
 
     def source_of(self, i: int) -> int:
-        """The layer whose tensors layer i runs."""
-        return int(self.layers[i].get("weights_of", i))
+        """The layer whose tensors layer i runs (through any chain of `weights_of`)."""
+        seen = {i}
+        while "weights_of" in self.layers[i]:
+            i = int(self.layers[i]["weights_of"])
+            if i in seen:
+                raise ModelConfigError(f"layer {i}: weights_of runs in a circle")
+            seen.add(i)
+        return i
 
     def validate(self) -> None:
         if self.vocab < 1 or self.width < 1 or not self.layers:
@@ -68,8 +74,9 @@ class TigesunConfig:
             m = layer["mixer"]
             if "weights_of" in layer:
                 j = layer["weights_of"]
-                if not isinstance(j, int) or not 0 <= j < i or "weights_of" in self.layers[j]:
-                    raise ModelConfigError(f"{where}: weights_of must name an earlier layer with tensors of its own")
+                if not isinstance(j, int) or not 0 <= j < len(self.layers) or j == i:
+                    raise ModelConfigError(f"{where}: weights_of must name another layer")
+                j = self.source_of(i)
                 mine = {k: v for k, v in layer.items() if k != "weights_of"}
                 if mine != self.layers[j]:
                     raise ModelConfigError(f"{where}: a layer that runs layer {j}'s tensors must have layer {j}'s sizes")

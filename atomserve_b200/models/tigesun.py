@@ -48,10 +48,9 @@ def _mixer(c: TigesunConfig, layer: dict, prefix: str) -> PartSpec:
 
 
 def build_spec(c: TigesunConfig) -> ModelSpec:
-    layers, schedule, index_of = [], [], {}
+    layers, index_of = [], {}
     for i, layer in enumerate(c.layers):
-        j = c.source_of(i)
-        if j == i:
+        if c.source_of(i) == i:
             p = f"l{i}."
             mlp = layer.get("mlp")
             index_of[i] = len(layers)
@@ -64,7 +63,7 @@ def build_spec(c: TigesunConfig) -> ModelSpec:
                 feed_forward_norm=(PartSpec("sandwich_norm", dict(eps=c.norm_eps, tensor=p + "norm2", out_tensor=p + "norm2b"))
                                    if mlp is not None else PartSpec("none")),
             ))  # fmt: skip
-        schedule.append(LayerCall(index_of[j]))
+    schedule = [LayerCall(index_of[c.source_of(i)]) for i in range(len(c.layers))]
     return ModelSpec(
         hidden_size=c.width,
         vocab_size=c.vocab,

@@ -53,8 +53,8 @@ class ScaledRotary(Rotary):
     def __init__(self, hidden_size: int, prefix: str, head_dim: int, theta: float, factor: float, original: float,
                  fast: float, slow: float, rotary_dim: int | None = None, pairing: str = "half"):  # fmt: skip
         super().__init__(hidden_size, prefix, head_dim, theta, rotary_dim, pairing)
-        if not factor >= 1.0 or not original > 0 or not fast > 0 or not slow > 0:
-            raise ValueError("a scaled rotary encoding needs factor >= 1 and positive original, fast and slow")
+        if not factor > 0 or not original > 0 or not fast > 0 or not slow > 0:
+            raise ValueError("a scaled rotary encoding needs positive factor, original, fast and slow")
         self.factor, self.original, self.fast, self.slow = float(factor), float(original), float(fast), float(slow)
         self.magnitude = 0.1 * math.log(self.factor) + 1.0
 

@@ -790,6 +790,162 @@ def time_zogepel(widths: list[int], layers: int, steps: int, warmup: int, pk: di
         print(json.dumps(line), flush=True)
 
 
+# ---- the Tigesun design beside Zogepel at equal width (`--only tigesun`) --------------------------
+
+def tigesun_shape(width: int, layers: int) -> dict:
+    """Layer sizes that resemble a served model's: attention with heads of 128, four query heads a kv
+    head and a stretched rotation of the whole head; a state-space layer twice the width inside, in
+    heads of 64 with a state of 128 in eight groups and four taps; attention over a latent of 512 in
+    a window of 1,024; a feed-forward of four times the width after the attention layers."""
+    heads = width // 128
+    rot = dict(base=1000000.0, dims=128, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0))
+    kinds = [
+        dict(type="attention", mixer=dict(heads=heads, kv_heads=max(heads // 4, 1), dim=128, vdim=128, scale=128 ** -0.5, rot=rot),
+             mlp=dict(kind="dense", ff=4 * width)),
+        dict(type="mamba2", mixer=dict(heads=2 * width // 64, vdim=64, state=128, groups=8, conv=4, norm_groups=8), mlp=None),
+        dict(type="latent_attention", mixer=dict(heads=heads, dim=128, vdim=128, kv_rank=512, scale=128 ** -0.5, mask=dict(size=1024)),
+             mlp=dict(kind="dense", ff=4 * width)),
+        dict(type="mamba2", mixer=dict(heads=2 * width // 64, vdim=64, state=128, groups=8, conv=4, norm_groups=8), mlp=None),
+    ]  # fmt: skip
+    return dict(architecture="Tigesun", vocab=32000, width=width, layers=[kinds[i % 4] for i in range(layers)], norm=dict(eps=1e-6),
+                logit_softcap=30.0)  # fmt: skip
+
+
+def time_tigesun(widths: list[int], layers: int, steps: int, warmup: int, pk: dict) -> None:
+    """Prefill and decode of a Tigesun model and of a Zogepel model of the same width and depth
+    (random weights), through the step function, and the design's own kernels one by one against
+    their rooflines beside the like kernels of Zogepel, Gefilix and Qwen3."""
+    import torch
+
+    from atomserve_b200 import ops
+
+    timed, model_times = design_timers(steps, warmup)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
+    bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    bf = torch.bfloat16
+    for width in widths:
+        line = {"only": "tigesun", "width": width, "layers": layers, "peaks": pk["source"],
+                "tigesun": model_times(tigesun_shape(width, layers), 32000), "zogepel": model_times(zogepel_shape(width, layers), 32000)}
+        kern = {}
+        T, B, ctx, bs = PROMPT_TOKENS, 64, PROMPT_TOKENS, BLOCK_SIZE
+        # the state-space recurrence (state 128 x 64 a head, B and C shared by the heads of a group) beside the
+        # matrix memory of Zogepel (64 x 128 a head): one request of T tokens (in segments), B requests of one token
+        H, N, P, G, K = 2 * width // 64, 128, 64, 8, 4
+        inner, C = H * P, H * P + 2 * G * N
+        proj = torch.randn(T, 2 * inner + 2 * G * N + H, device="cuda", dtype=bf)
+        taps, bias = torch.randn(C, K, device="cuda") * 0.5, torch.zeros(C, device="cuda")
+        zero = torch.zeros(H, device="cuda")
+        state, conv_state = torch.zeros(B, H, N, P, device="cuda"), torch.zeros(B, K - 1, C, device="cuda")
+        segments = ops.plan_segments([T], proj.device)
+        one, each = (i32([0]), i32([0, T])), (i32(list(range(B))), i32(list(range(B + 1))))
+        Hm, Dm, Vm = width // 128, 64, 128
+        proj_m = torch.randn(T, 2 * Hm * Dm + 2 * Hm * Vm, device="cuda", dtype=bf)
+        zm, zero_m = torch.randn(T, 2 * Hm, device="cuda"), torch.zeros(Hm, device="cuda")
+        state_m, norm_m, top_m = torch.zeros(B, Hm, Dm, Vm, device="cuda"), torch.zeros(B, Hm, Dm, device="cuda"), torch.zeros(B, Hm, device="cuda")
+
+        def conv(rows, slots, starts, n):
+            return ops.conv_steps(proj[:rows], inner, 2 * inner + 2 * G * N, taps, bias, conv_state, zero, zero, slots, starts, n)
+
+        xbc, decay, weight = conv(T, *one, 1)
+
+        def recurrence(rows, slots, starts, n, seg):
+            return ops.linear_recurrence(xbc[:rows], inner + G * N, inner, 0, state, slots, starts, n, token_decay=decay[:rows],
+                                         token_gain=weight[:rows], qk_share=H // G, segments=seg)  # fmt: skip
+
+        def memory(rows, slots, starts, n, seg):
+            a, b, _ = ops.capped_gates_scan(zm[:rows], 0, Hm, Hm, zero_m, zero_m, 15.0, top_m, slots, starts, n)
+            return ops.linear_recurrence(proj_m[:rows], 0, Hm * Dm, 2 * Hm * Dm, state_m, slots, starts, n, token_decay=a, token_gain=b,
+                                         norm_state=norm_m, q_scale=Dm ** -0.5, segments=seg)  # fmt: skip
+
+        for name, fn, flops, cells in (("state_space", recurrence, 4.0 * H * N * P, H * N * P), ("matrix_memory", memory, 4.0 * Hm * Dm * (Vm + 1), Hm * Dm * (Vm + 1))):
+            ms = timed(lambda: fn(T, *one, 1, segments), 8)
+            kern[f"{name}_prefill"] = {"ms": round(ms, 4), "gflops": round(T * flops / ms / 1e6, 1), "note": "float32 CUDA cores"}
+            ms = timed(lambda: fn(B, *each, B, None))
+            kern[f"{name}_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(2.0 * B * cells * 4 / (ms * 1e-3) / bw, 3)}
+        # the convolution with the step sizes, its state, and the gated norm in parts: bytes moved over the measured copy bandwidth
+        for name, rows, slots_starts, n in (("prefill", T, one, 1), ("decode_b64", B, each, B)):
+            ms = timed(lambda: conv(rows, *slots_starts, n))
+            kern[f"conv_steps_{name}"] = {"ms": round(ms, 4), "hbm_frac": round(rows * (C * 4 + H * 10) / (ms * 1e-3) / bw, 3)}
+            ms = timed(lambda: ops.conv_state_update(conv_state, proj[:rows], inner, *slots_starts, n))
+            kern[f"conv_state_update_{name}"] = {"ms": round(ms, 4)}
+        y = torch.randn(T, inner, device="cuda")
+        gain_i = torch.ones(inner, device="cuda")
+        ms = timed(lambda: ops.gate_group_norm(y, xbc[:, :inner], proj[:, :inner], zero, gain_i, 8, P, 1e-6))
+        kern["gate_group_norm"] = {"ms": round(ms, 4), "hbm_frac": round(T * inner * 10 / (ms * 1e-3) / bw, 3)}
+        gate = torch.randn(T, inner, device="cuda", dtype=bf)
+        ms = timed(lambda: ops.head_norm_gate(y, gate, H, gain=gain_i, eps=1e-6))
+        kern["head_norm_gate"] = {"ms": round(ms, 4), "hbm_frac": round(T * inner * 8 / (ms * 1e-3) / bw, 3)}
+        # the norms around a sublayer beside Zogepel's norm on a sublayer's output, T rows
+        x, yw = torch.randn(T, width, device="cuda"), torch.randn(T, width, device="cuda")
+        gain = torch.ones(width, device="cuda")
+        ms = timed(lambda: ops.add_normed(x, yw, gain, 1e-6, gain, 1e-6, bf, gain))
+        kern["add_normed"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 14 / (ms * 1e-3) / bw, 3)}
+        ms = timed(lambda: ops.residual_out_norm(x, yw, gain, 1e-6, bf, mult=0.5, scale=gain))
+        kern["residual_out_norm"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 14 / (ms * 1e-3) / bw, 3)}
+        # the feed-forward's inner half: product and activation, beside Qwen3's SwiGLU and Zogepel's squared ReLU at equal size
+        F = 4 * width
+        h = torch.randn(T, width, device="cuda", dtype=bf)
+        w_gu, b_gu = torch.randn(2 * F, width, device="cuda", dtype=bf) * 0.02, torch.zeros(2 * F, device="cuda")
+        part = tigesun_inner(width, F, w_gu, b_gu)
+        for name, rows, n in (("prefill", T, 4), ("decode_b64", B, steps)):
+            flops = 4.0 * rows * F * width
+            ms = timed(lambda: part.inner(h[:rows]), n)
+            kern[f"gated_gelu_inner_{name}"] = {"ms": round(ms, 4), "tc_frac": round(flops / (ms * 1e-3) / tf, 4), "hbm_frac": round(2.0 * F * width * 2 / (ms * 1e-3) / bw, 3)}
+            ms = timed(lambda: ops.linear_swiglu(h[:rows], w_gu), n)
+            kern[f"swiglu_inner_{name}"] = {"ms": round(ms, 4), "tc_frac": round(flops / (ms * 1e-3) / tf, 4), "hbm_frac": round(2.0 * F * width * 2 / (ms * 1e-3) / bw, 3)}
+        # attention: causal with heads of 128 (the kernels Qwen3 runs), and over a latent of 512 in a window of 1,024
+        # beside Gefilix's latent of 512 + 64 without a window (the decode reads 1,024 latents instead of the context)
+        Ha, KV, hd, R, window = width // 128, max(width // 512, 1), 128, 512, 1024
+        pages_per = ctx // bs
+        tables = i32([[r * pages_per + j for j in range(pages_per)] for r in range(B)])
+        starts, at = i32(list(range(B + 1))), i32([ctx - 1] * B)
+        t1 = i32([list(range(pages_per))])
+        lat = torch.randn(B * pages_per, 1, bs, R, device="cuda", dtype=bf)
+        lat_g = torch.randn(B * pages_per, 1, bs, R + 64, device="cuda", dtype=bf)
+        for name, pages, rk, win, keys in (("windowed_latent_attention", lat, R, window, window), ("latent_attention", lat_g, R, None, ctx)):
+            q_lat = torch.randn(B, Ha, pages.shape[3], device="cuda")
+            ms = timed(lambda: ops.latent_attention(q_lat, pages, tables, starts, at, rank=rk, num_requests=B, max_context=ctx, scale=0.07, window=win))
+            kern[f"{name}_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(B * keys * pages.shape[3] * 2 / (ms * 1e-3) / bw, 3)}
+            q_lat = torch.randn(T, Ha, pages.shape[3], device="cuda")
+            seen = sum(min(t + 1, keys) for t in range(T))
+            ms = timed(lambda: ops.latent_attention(q_lat, pages, t1, i32([0, T]), i32([0]), rank=rk, num_requests=1, max_context=T, scale=0.07, window=win), 4)
+            kern[f"{name}_prefill"] = {"ms": round(ms, 3), "tc_frac": round(2.0 * seen * Ha * (pages.shape[3] + rk) / (ms * 1e-3) / tf, 4)}
+        k_pages = torch.randn(B * pages_per, KV, bs, hd, device="cuda", dtype=bf)
+        v_pages = torch.randn_like(k_pages)
+        q = torch.randn(B, Ha, hd, device="cuda", dtype=bf)
+        ms = timed(lambda: ops.paged_attention(q, k_pages, v_pages, tables, starts, at, num_requests=B, max_context=ctx, window=None,
+                                               scale=0.088, host_q_lens=[1] * B))  # fmt: skip
+        kern["paged_attention_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(2.0 * B * ctx * KV * hd * 2 / (ms * 1e-3) / bw, 3)}
+        qp = torch.randn(T, Ha, hd, device="cuda", dtype=bf)
+        ms = timed(lambda: ops.paged_attention(qp, k_pages, v_pages, t1, i32([0, T]), i32([0]), num_requests=1, max_context=T, window=None,
+                                               scale=0.088, host_q_lens=[T]), 4)  # fmt: skip
+        kern["paged_attention_prefill"] = {"ms": round(ms, 3), "tc_frac": round(4.0 * T * T / 2 * Ha * hd / (ms * 1e-3) / tf, 4)}
+        # q/k norm, stretched rotation and page write (the kernel Qwen3 runs, with other frequencies and gains)
+        qk = torch.randn(T, (Ha + 2 * KV) * hd, device="cuda", dtype=bf)
+        g1, positions, slots = torch.ones(hd, device="cuda"), i32(list(range(T))), i32(list(range(T)))
+        inv_freq = (1.0 / 1000000.0 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd)).cuda()
+        ms = timed(lambda: ops.qk_norm_rope_store(qk, Ha, KV, hd, positions, q_gain=g1, k_gain=g1, eps=1e-6, inv_freq=inv_freq,
+                                                  rotary_dim=hd, slots=slots, k_cache=k_pages, v_cache=v_pages))  # fmt: skip
+        kern["qk_norm_rope_store"] = {"ms": round(ms, 4), "hbm_frac": round(T * (2 * Ha + 4 * KV) * hd * 2 / (ms * 1e-3) / bw, 3)}
+        logits = torch.randn(B, 32000, device="cuda")
+        ms = timed(lambda: ops.softcap_(logits, 30.0))
+        kern["softcap_b64"] = {"ms": round(ms, 4), "hbm_frac": round(B * 32000 * 8 / (ms * 1e-3) / bw, 3)}
+        line["kernels"] = kern
+        print(json.dumps(line), flush=True)
+
+
+def tigesun_inner(width: int, ff: int, w_gu, b_gu):
+    """A gated feed-forward part holding the given stacked gate and up rows ([2 ff, width], gate first)."""
+    import torch
+
+    from atomserve_b200.parts import PartSpec, build_part
+
+    part = build_part("feed_forward", PartSpec("gated_mlp", dict(intermediate_size=ff, activation="gelu_tanh", biases=True), "f."), width)
+    part.load({"f.gate": w_gu[:ff], "f.up": w_gu[ff:], "f.down": torch.zeros(8, ff, device=w_gu.device, dtype=w_gu.dtype), "f.gate.b": b_gu[:ff],
+               "f.up.b": b_gu[ff:], "f.down.b": torch.zeros(8, device=w_gu.device)})  # fmt: skip
+    return part
+
+
 def reference_arm(args) -> int:
     """The same measurement on the unmodified reference (baseline/reference_arm.py): its own
     engine, sampler and PyTorch model code on this GPU, nothing of this package."""
@@ -845,7 +1001,7 @@ def main() -> int:
                         help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling", "designs", "zogepel"], help="time just this (for profiling small cases and the other shapes)")
+    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling", "designs", "zogepel", "tigesun"], help="time just this (for profiling small cases and the other shapes)")
     parser.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="with --only decode/prefill/serve: layer sizes of Qwen3-8B, -14B or -32B")
     parser.add_argument("--context", type=int, default=PROMPT_TOKENS, help="with --only decode: tokens each request holds when decoding starts")
     parser.add_argument("--requests", type=int, default=32, help="with --only serve: requests submitted at once")
@@ -853,7 +1009,7 @@ def main() -> int:
     parser.add_argument("--budget", type=int, default=512, help="with --only serve: the scheduler's token budget per step")
     parser.add_argument("--gemm-shape", default="all", help="with --only gemm: qkv, o, gate_up, down, lm_head or all")
     parser.add_argument("--gemm-tokens", default="1,8,64,2048", help="with --only gemm: token counts, comma-separated")
-    parser.add_argument("--widths", default="2048,4096", help="with --only designs or zogepel: model widths, comma-separated")
+    parser.add_argument("--widths", default="2048,4096", help="with --only designs, zogepel or tigesun: model widths, comma-separated")
     parser.add_argument("--timeline", action="store_true", help="with --only gemm: where a decode-size call's time goes")
     args = parser.parse_args()
     args.layers_given = any(a == "--layers" or a.startswith("--layers=") for a in sys.argv[1:])
@@ -881,6 +1037,9 @@ def main() -> int:
         return 0
     if args.only == "zogepel":
         time_zogepel([int(w) for w in args.widths.split(",")], args.layers if args.layers_given else 4, max(args.steps // 4, 8), warmup, pk)
+        return 0
+    if args.only == "tigesun":
+        time_tigesun([int(w) for w in args.widths.split(",")], args.layers if args.layers_given else 4, max(args.steps // 4, 8), warmup, pk)
         return 0
     if args.only == "gemm" and args.timeline:
         gemm_timelines(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")])

@@ -94,8 +94,10 @@ def test_stretched_frequencies(dims, base, scaling):
     (lambda c: c["layers"][0]["mixer"].__setitem__("groups", 3), "groups"),
     (lambda c: c["layers"][0]["mixer"].pop("state"), "state"),
     (lambda c: c["layers"][0]["mlp"].__setitem__("kind", "moe"), "dense"),
-    (lambda c: c["layers"][3].__setitem__("weights_of", 5), "weights_of"),
-    (lambda c: c["layers"][4].__setitem__("weights_of", 3), "weights_of"),
+    (lambda c: c["layers"][3].__setitem__("weights_of", 9), "weights_of"),
+    (lambda c: c["layers"][4].__setitem__("weights_of", 4), "weights_of"),
+    (lambda c: c["layers"][2].__setitem__("weights_of", 6), "circle"),
+    (lambda c: c["layers"][4].__setitem__("weights_of", 3), "sizes"),
     (lambda c: c["layers"][3].__setitem__("mixer", dict(c["layers"][3]["mixer"], heads=4)), "sizes"),
     (lambda c: c.pop("norm"), "norm"),
     (lambda c: c.__setitem__("logit_softcap", -1.0), "logit_softcap"),
@@ -107,3 +109,11 @@ def test_rejections(change, text):
     change(raw)
     with pytest.raises(ModelConfigError, match=text):
         parse(raw)
+
+
+def test_a_chain_of_layers_that_run_anothers_tensors():
+    raw = copy.deepcopy(TIGESUN["a"][0])
+    raw["layers"][6]["weights_of"] = 3  # 6 -> 3 -> 2
+    arch, config = parse(raw)
+    assert [config.source_of(i) for i in range(7)] == [0, 1, 2, 2, 0, 1, 2]
+    assert [call.layer for call in arch.build_spec(config).schedule] == [0, 1, 2, 2, 0, 1, 2]

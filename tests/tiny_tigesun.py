@@ -63,7 +63,7 @@ TIGESUN_B = _model(257, 64, 1e-6, None, [
 BLOCK_SIZE_B = 8
 
 # sizes at which the bfloat16 products and attention run this package's tensor-core kernels
-TIGESUN_C = _model(640, 256, 2e-6, 30.0, [
+TIGESUN_C = _model(704, 256, 2e-6, 30.0, [
     attention(8, 2, 128, 128, 0.2, 10000.0, 64, scaling=(8.0, 128, 16.0, 2.0), ff=512),
     mamba2(8, 64, 128, 1, 4, 1),
     latent(4, 64, 128, 64, 100, 0.2, ff=384),
