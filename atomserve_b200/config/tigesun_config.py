@@ -54,7 +54,7 @@ class TigesunConfig:
     def source_of(self, i: int) -> int:
         """The layer whose tensors layer i runs (through any chain of `weights_of`)."""
         seen = {i}
-        while "weights_of" in self.layers[i]:
+        while self.layers[i].get("weights_of") is not None:
             i = int(self.layers[i]["weights_of"])
             if i in seen:
                 raise ModelConfigError(f"layer {i}: weights_of runs in a circle")
@@ -72,13 +72,12 @@ class TigesunConfig:
             where = f"layer {i}"
             _need(layer, ("type", "mixer"), where)
             m = layer["mixer"]
-            if "weights_of" in layer:
+            if layer.get("weights_of") is not None:
                 j = layer["weights_of"]
                 if not isinstance(j, int) or not 0 <= j < len(self.layers) or j == i:
                     raise ModelConfigError(f"{where}: weights_of must name another layer")
                 j = self.source_of(i)
-                mine = {k: v for k, v in layer.items() if k != "weights_of"}
-                if mine != self.layers[j]:
+                if any(layer.get(k) != self.layers[j].get(k) for k in ("type", "mixer", "mlp")):
                     raise ModelConfigError(f"{where}: a layer that runs layer {j}'s tensors must have layer {j}'s sizes")
             if layer["type"] == "attention":
                 _need(m, ("heads", "kv_heads", "dim", "vdim", "scale"), where + " mixer")

@@ -39,6 +39,7 @@
 
 #include "common.cuh"
 #include "gemm_partials.cuh"
+#include "glu.cuh"
 #include "tcgen05.cuh"
 
 // How the pair kernel cuts its last round of tiles along K (gemm_tcgen05_pair.cu).
@@ -63,6 +64,8 @@ struct GemmParams {
   const void* residual;  // bf16 [M, N] or null
   float* workspace;      // f32 [tiles][max_slots][128][BN] partial sums (stream schedule)
   int* status;           // device word, set non-zero by a wait that ran out
+  const float* glu_bias; // kStoreSwiGLU: float32 [N] in the weight rows' alternating order, or null
+  int glu_act;           // kStoreSwiGLU: the gate's activation (asb::GluAct)
   int p_rows, q_rows;    // rows of P and Q (M and N, or N and M when swapped)
   int ldo;               // row stride of out (N)
   int swap;              // 1: P = w (lanes are output columns), Q = x
@@ -164,8 +167,8 @@ struct Config {
   static constexpr int kMaxStages = 12;   // the barriers' 256 bytes hold 2 * 12 + 4 of them and the tensor-memory slot
 };
 
-// SwiGLU on a (gate, up) pair of float32 sums (atomserve/kernels.py:437-449).
-__device__ __forceinline__ float swiglu(float gate, float up) { return gate / (1.f + __expf(-gate)) * up; }
+// The gated unit on a (gate, up) pair of float32 sums is asb::glu_pair (glu.cuh); without a bias and with
+// the SiLU it is SwiGLU (atomserve/kernels.py:437-449).
 __device__ __forceinline__ float relu2(float v) { v = fmaxf(v, 0.f); return v * v; }  // kStoreBf16Relu2: max(v, 0)^2 on the float32 sums
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -368,7 +371,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
               const float up = __shfl_down_sync(0xffffffffu, __uint_as_float(raw[j]), 1);
               const int tok = q0 + c + j;
               if ((lane & 1) == 0 && prow < p.p_rows && tok < p.q_rows)
-                ((__nv_bfloat16*)p.out)[(size_t)tok * (p.ldo / 2) + prow / 2] = __float2bfloat16_rn(swiglu(__uint_as_float(raw[j]), up));
+                ((__nv_bfloat16*)p.out)[(size_t)tok * (p.ldo / 2) + prow / 2] =
+                    __float2bfloat16_rn(asb::glu_pair(__uint_as_float(raw[j]), up, p.glu_bias, prow, p.glu_act));
             }
           } else if (prow < p.p_rows) {
             // columns are weight rows: this thread holds kChunk / 2 (gate, up) pairs of its token
@@ -377,8 +381,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             uint4 packed[kChunk / 16];
             __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(packed);
 #pragma unroll
-            for (int j = 0; j < kChunk / 2; ++j)
-              ob[j] = __float2bfloat16_rn(swiglu(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1])));
+            for (int j = 0; j < kChunk / 2; ++j)  // (columns past the last weight row read no bias)
+              ob[j] = __float2bfloat16_rn(asb::glu_pair(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1]),
+                                                        j < valid ? p.glu_bias : nullptr, q0 + c + 2 * j, p.glu_act));
             if (valid == kChunk / 2 && (((uintptr_t)o) & 15) == 0) {
 #pragma unroll
               for (int v = 0; v < kChunk / 16; ++v) *reinterpret_cast<uint4*>(o + 8 * v) = packed[v];
@@ -520,7 +525,7 @@ __global__ void segment_reduce_kernel(const GemmParams p, int parts) {
       const int prow = p0 + row, qrow = q0 + col;
       if (prow >= p.p_rows || qrow >= p.q_rows) continue;
       const size_t at = (size_t)qrow * (p.ldo / 2) + prow / 2;
-      ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(swiglu(e[k], e[k + 1]));
+      ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(asb::glu_pair(e[k], e[k + 1], p.glu_bias, prow, p.glu_act));
     }
     return;
   }
@@ -728,7 +733,8 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, co
 
 // The form for many tokens on pairs of SMs (gemm_tcgen05_pair.cu).
 extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, const void* residual, int M, int N,
-                                     int K, int mode, int bn, float* workspace, int* status, cudaStream_t stream);
+                                     int K, int mode, int bn, float* workspace, int* status, const float* glu_bias,
+                                     int glu_act, cudaStream_t stream);
 
 // Float32 workspace elements a call needs (0 when every tile is computed whole).
 extern "C" long long asb_gemm_tcgen05_workspace(int M, int N, int K, int* stream_out) {
@@ -778,9 +784,10 @@ extern "C" int asb_gemm_tcgen05_plan(int M, int N, int K, int* out8) {
 // up (row 2i gate_i, row 2i + 1 up_i) and out is bfloat16 [M, N / 2] = silu(gate) * up; 3: no out:
 // the product stays in the workspace as float32 partial sums for a consumer kernel to add up
 // (only for shapes whose plan cuts K with swapped operands, and then tiles_q is 1).
-extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const void* residual, int M,
-                                int N, int K, int mode, float* workspace, int* status,
-                                cudaStream_t stream) {
+// glu_bias, glu_act: mode 2 as act(gate + bias) * (up + bias) with another activation (asb::GluAct) and a
+// float32 bias [N] in the weight rows' alternating order (or null).
+static int gemm_tcgen05_run(void* out, const void* x, const void* w, const void* residual, int M, int N, int K, int mode,
+                            float* workspace, int* status, const float* glu_bias, int glu_act, cudaStream_t stream) {
   const int out_f32 = mode == 1;
   if (mode < 0 || mode > 4) return asb::fail("gemm_tcgen05: unknown mode %d", mode);
   if (mode == 4 && residual) return asb::fail("gemm_tcgen05: the squared-ReLU form takes no residual");
@@ -795,7 +802,7 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   if (mode == 3 && !(pl.stream && pl.swap && pl.tiles_q == 1))
     return asb::fail("gemm_tcgen05: [%d, %d] x [%d, %d] does not run with partial sums", M, K, N, K);
   if (pl.pair && mode != 3)
-    return asb_gemm_tcgen05_pair(out, x, w, residual, M, N, K, mode, pl.pair, workspace, status, stream);
+    return asb_gemm_tcgen05_pair(out, x, w, residual, M, N, K, mode, pl.pair, workspace, status, glu_bias, glu_act, stream);
   if (pl.workspace > 0 && !workspace) return asb::fail("gemm_tcgen05: this shape needs a workspace of %lld floats", pl.workspace);
 
   GemmParams p;
@@ -803,6 +810,8 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
   p.residual = residual;
   p.workspace = workspace;
   p.status = status;
+  p.glu_bias = glu_bias;
+  p.glu_act = glu_act;
   p.swap = pl.swap;
   p.ldo = N;
   p.p_rows = pl.swap ? N : M;
@@ -827,4 +836,19 @@ extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const v
     case 128: return launch<128>(mp, mq, p, pl, stream);
     default: return launch<256>(mp, mq, p, pl, stream);
   }
+}
+
+extern "C" int asb_gemm_tcgen05(void* out, const void* x, const void* w, const void* residual, int M,
+                                int N, int K, int mode, float* workspace, int* status,
+                                cudaStream_t stream) {
+  return gemm_tcgen05_run(out, x, w, residual, M, N, K, mode, workspace, status, nullptr, asb::kGluSilu, stream);
+}
+
+// out bfloat16 [M, N / 2] = act(x . gate^T + b_gate) * (x . up^T + b_up): mode 2 of asb_gemm_tcgen05 with the
+// activation `act` (asb::GluAct: 0 SiLU, 1 the tanh form of GELU, 2 the exact GELU) and `bias`, float32 [N] in
+// the alternating order of w's rows, or null.
+extern "C" int asb_gemm_tcgen05_glu(void* out, const void* x, const void* w, const float* bias, int act, int M, int N,
+                                    int K, float* workspace, int* status, cudaStream_t stream) {
+  if (act < 0 || act > 2) return asb::fail("gemm_tcgen05_glu: activation %d", act);
+  return gemm_tcgen05_run(out, x, w, nullptr, M, N, K, 2, workspace, status, bias, act, stream);
 }

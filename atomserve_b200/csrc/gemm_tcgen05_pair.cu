@@ -23,6 +23,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "glu.cuh"
 #include "tcgen05.cuh"
 
 namespace {
@@ -41,6 +42,8 @@ struct PairParams {
   void* out;             // bf16 [M, N], f32 [M, N], or bf16 [M, N / 2] (SwiGLU)
   const void* residual;  // bf16 [M, N] or null
   int* status;
+  const float* glu_bias;  // kStoreSwiGLU: float32 [N] in the weight rows' alternating order, or null
+  int glu_act;            // kStoreSwiGLU: the gate's activation (asb::GluAct)
   int M, N, ldo;
   int epilogue;
   int bn;                  // weight rows per tile: a multiple of 32, at most the kernel's BN
@@ -77,7 +80,6 @@ struct PairConfig {
   static_assert(kLoaders >= 1 && kLoaders <= kStages, "a loader's step must stay inside the ring of stages");
 };
 
-__device__ __forceinline__ float swiglu(float gate, float up) { return gate / (1.f + __expf(-gate)) * up; }
 __device__ __forceinline__ float relu2(float v) { v = fmaxf(v, 0.f); return v * v; }  // kStoreBf16Relu2
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -328,7 +330,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           uint4 packed[2];
           __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(packed);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) ob[j] = __float2bfloat16_rn(swiglu(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1])));
+          for (int j = 0; j < 16; ++j)  // (columns past the last weight row read no bias)
+            ob[j] = __float2bfloat16_rn(asb::glu_pair(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1]),
+                                                      2 * j < valid ? p.glu_bias : nullptr, n0 + c + 2 * j, p.glu_act));
           if (valid == 32 && (((uintptr_t)o) & 15) == 0) {
             *reinterpret_cast<uint4*>(o) = packed[0];
             *reinterpret_cast<uint4*>(o + 8) = packed[1];
@@ -427,7 +431,7 @@ __global__ void tail_reduce_kernel(const PairParams p) {
     __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * (p.ldo / 2) + n / 2;
 #pragma unroll
     for (int k = 0; k < 4; k += 2)
-      if (n + k + 1 < p.N) o[k / 2] = __float2bfloat16_rn(swiglu(e[k], e[k + 1]));
+      if (n + k + 1 < p.N) o[k / 2] = __float2bfloat16_rn(asb::glu_pair(e[k], e[k + 1], p.glu_bias, n + k, p.glu_act));
     return;
   }
   const size_t at = (size_t)row * p.ldo + n;
@@ -532,7 +536,8 @@ extern "C" long long asb_gemm_tcgen05_pair_cut(int M, int N, int K, int bn, int*
 // rows, runs those: narrower tiles let one round of them occupy more pairs of SMs).
 // workspace: float32, asb_gemm_tcgen05_pair_cut(M, N, K, bn) elements (null if that is 0).
 extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, const void* residual, int M, int N,
-                                     int K, int mode, int bn, float* workspace, int* status, cudaStream_t stream) {
+                                     int K, int mode, int bn, float* workspace, int* status, const float* glu_bias,
+                                     int glu_act, cudaStream_t stream) {
   if (mode < 0 || mode == 3 || mode > 4) return asb::fail("gemm_tcgen05_pair: unknown mode %d", mode);
   if (mode == 4 && residual) return asb::fail("gemm_tcgen05_pair: the squared-ReLU form takes no residual");
   if (mode == 2 && (residual || N % 2)) return asb::fail("gemm_tcgen05_pair: the SwiGLU form takes no residual and an even N");
@@ -547,6 +552,8 @@ extern "C" int asb_gemm_tcgen05_pair(void* out, const void* x, const void* w, co
   p.out = out;
   p.residual = residual;
   p.status = status;
+  p.glu_bias = glu_bias;
+  p.glu_act = glu_act;
   p.M = M;
   p.N = N;
   p.ldo = N;

@@ -22,6 +22,7 @@ namespace {
 
 constexpr int kConvThreads = 128;
 constexpr int kConvTokens = 32;
+constexpr int kConvWindow = 8;  // taps up to which a thread keeps the convolution's window in registers
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -41,24 +42,27 @@ struct ConvParams {
   int stride, conv_off, dt_off, C, K, H, R;
 };
 
-// grid.x: token tiles of all requests (a request's tiles found by walking the requests), grid.y:
+// grid.x: token tiles of all requests (a block finds its request by bisection), grid.y:
 // chunks of 128 columns over the C channels followed by the H step columns.
 template <typename T>
 __global__ void __launch_bounds__(kConvThreads)
 conv_steps_kernel(const ConvParams p) {
   asb::pdl_wait();
   asb::pdl_launch_dependents();
-  int tile = blockIdx.x, r = 0, q_len = 0;
-  for (; r < p.R; ++r) {
-    q_len = p.req_q_start[r + 1] - p.req_q_start[r];
-    const int tiles = (q_len + kConvTokens - 1) / kConvTokens;
-    if (tile < tiles) break;
-    tile -= tiles;
+  // request r's tiles are the blocks from first_r = req_q_start[r] / kConvTokens + r on: first_(r+1) - first_r
+  // is at least the tiles r needs, so the ranges do not meet, and the last is below the grid's
+  // tokens / kConvTokens + R. The block's request: the last r with first_r <= blockIdx.x, by bisection.
+  int lo = 0, hi = p.R - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (p.req_q_start[mid] / kConvTokens + mid <= (int)blockIdx.x) lo = mid;
+    else hi = mid - 1;
   }
-  if (r == p.R) return;
+  const int r = lo, row_lo = p.req_q_start[r], q_len = p.req_q_start[r + 1] - row_lo;
+  const int tile = blockIdx.x - (row_lo / kConvTokens + r);
+  if (tile < 0 || tile * kConvTokens >= q_len) return;
   const int c = blockIdx.y * kConvThreads + threadIdx.x;
   if (c >= p.C + p.H) return;
-  const int row_lo = p.req_q_start[r];
   const int q0 = tile * kConvTokens, nq = min(kConvTokens, q_len - q0);
   const T* proj = (const T*)p.proj;
   if (c >= p.C) {
@@ -78,6 +82,38 @@ conv_steps_kernel(const ConvParams p) {
   const float* held = p.conv_state + (size_t)p.state_slots[r] * (K - 1) * p.C + c;
   const T* in = proj + p.conv_off + c;
   T* out = (T*)p.out;
+  if (K <= kConvWindow) {
+    // Up to kConvWindow taps: the taps padded in front with zeros to kConvWindow (a zero tap leaves the
+    // sum as it is, so the sum runs in the same order as below), the last kConvWindow - 1 inputs kept in
+    // registers, and kConvWindow tokens at a time: their loads are in flight together, and each input
+    // is read once.
+    float w8[kConvWindow], hist[kConvWindow - 1];
+#pragma unroll
+    for (int j = 0; j < kConvWindow; ++j) w8[j] = j >= kConvWindow - K ? w[j - (kConvWindow - K)] : 0.f;
+#pragma unroll
+    for (int i = 0; i < kConvWindow - 1; ++i) {
+      const int at = q0 - (kConvWindow - 1) + i;  // negative: before the portion, K - 1 of them in the state
+      hist[i] = at >= 0 ? asb::to_float(in[(size_t)(row_lo + at) * p.stride]) : (K - 1 + at >= 0 ? held[(size_t)(K - 1 + at) * p.C] : 0.f);
+    }
+    for (int q = q0; q < q0 + nq; q += kConvWindow) {
+      float x[2 * kConvWindow - 1];
+#pragma unroll
+      for (int i = 0; i < kConvWindow - 1; ++i) x[i] = hist[i];
+#pragma unroll
+      for (int i = 0; i < kConvWindow; ++i)
+        x[kConvWindow - 1 + i] = q + i < q0 + nq ? asb::to_float(in[(size_t)(row_lo + q + i) * p.stride]) : 0.f;
+#pragma unroll
+      for (int i = 0; i < kConvWindow; ++i) {
+        float acc = b;
+#pragma unroll
+        for (int j = 0; j < kConvWindow; ++j) acc = fmaf(w8[j], x[i + j], acc);
+        if (q + i < q0 + nq) out[(size_t)(row_lo + q + i) * p.C + c] = asb::from_float<T>(silu_f(acc));
+      }
+#pragma unroll
+      for (int i = 0; i < kConvWindow - 1; ++i) hist[i] = x[kConvWindow + i];
+    }
+    return;
+  }
   for (int q = q0; q < q0 + nq; ++q) {
     float acc = b;
     for (int j = 0; j < K; ++j) {

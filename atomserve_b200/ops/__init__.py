@@ -18,7 +18,7 @@ from atomserve_b200.ops.latent import head_matmul, head_matmul_on_tensor_cores, 
 from atomserve_b200.ops.library import KernelLibraryError, require_device
 from atomserve_b200.ops.outnorm import capped_gates_scan, gated_token_slice, head_norm_gate, projection_norm_store, residual_out_norm
 from atomserve_b200.ops.recurrent import lightning_attention, linear_recurrence, plan_segments, rotary_table
-from atomserve_b200.ops.linear import PartialSums, interleave_gate_up, linear, linear_partial, linear_relu2, linear_swiglu, swiglu_fusable
+from atomserve_b200.ops.linear import PartialSums, interleave_gate_up, linear, linear_glu, linear_partial, linear_relu2, linear_swiglu, swiglu_fusable
 from atomserve_b200.ops.sandwich import add_normed, bias_glu, softcap_
 from atomserve_b200.ops.ssm import conv_state_update, conv_steps, gate_group_norm
 from atomserve_b200.ops.sampling import argmax_rows, presence_penalty, sample_rows
@@ -41,6 +41,7 @@ __all__ = [
     "interleave_gate_up",
     "linear",
     "linear_partial",
+    "linear_glu",
     "linear_relu2",
     "linear_swiglu",
     "paged_attention",

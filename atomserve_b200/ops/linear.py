@@ -204,6 +204,38 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
     return gemm_tcgen05(x, w_interleaved, None, torch.bfloat16, swiglu=True)
 
 
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu": 2}
+
+
+def linear_glu(x: torch.Tensor, w_interleaved: torch.Tensor, bias_interleaved: torch.Tensor | None, activation: str) -> torch.Tensor:
+    """act(x . gate^T + b_gate) * (x . up^T + b_up) in one kernel, as `linear_swiglu` with another
+    activation ("silu", "gelu_tanh" or "gelu") and a float32 bias [2I] in the order of the weight's
+    rows (gate_0, up_0, gate_1, ...), or None: biases and activation meet the float32 sums in the
+    tensor-core GEMM's epilogue, before the one rounding to bfloat16."""
+    require_cuda(x, w_interleaved, bias_interleaved)
+    if x.dtype != torch.bfloat16 or not swiglu_fusable(w_interleaved) or not x.is_contiguous() or x.data_ptr() % 16:
+        raise KernelLibraryError("linear_glu takes contiguous bfloat16 operands with K a multiple of 8")
+    if activation not in GLU_ACTIVATIONS:
+        raise KernelLibraryError(f"linear_glu: activation {activation!r} is not one of {sorted(GLU_ACTIVATIONS)}")
+    M, K = x.shape
+    N = w_interleaved.shape[0]
+    if x.dim() != 2 or w_interleaved.shape[1] != K or N % 2:
+        raise KernelLibraryError(f"linear_glu: x {tuple(x.shape)} does not match w {tuple(w_interleaved.shape)}")
+    b = bias_interleaved
+    if b is not None and (b.dtype != torch.float32 or b.shape != (N,) or not b.is_contiguous()):
+        raise KernelLibraryError(f"linear_glu: bias must be contiguous float32 [{N}]")
+    out = torch.empty(M, N // 2, device=x.device, dtype=torch.bfloat16)
+    need = _WORKSPACE_FLOATS.get((M, N, K))
+    if need is None:
+        query = lib().asb_gemm_tcgen05_workspace
+        query.restype = ctypes.c_longlong
+        need = _WORKSPACE_FLOATS[(M, N, K)] = query(M, N, K, None)
+    workspace = gemm_workspace(x.device, need) if need else None
+    check(lib().asb_gemm_tcgen05_glu(ptr(out), ptr(x), ptr(w_interleaved), ptr(b), GLU_ACTIVATIONS[activation], M, N, K,
+                                     ptr(workspace), ptr(gemm_status(x.device)), stream()))  # fmt: skip
+    return out
+
+
 def linear_relu2(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor | None:
     """max(x . w^T, 0)^2 in one kernel: the squared ReLU applied to the float32 sums in the
     tensor-core GEMM's epilogue, before the one rounding to bfloat16 (the unfused path rounds the

@@ -6,9 +6,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200.ops.library import KernelLibraryError, check, dtype_code, lib, ptr, require_cuda, stream
-from atomserve_b200.ops.linear import PartialSums
-
-GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu": 2}
+from atomserve_b200.ops.linear import GLU_ACTIVATIONS, PartialSums
 
 
 def add_normed(x: torch.Tensor, y: torch.Tensor | PartialSums, gain_out: torch.Tensor, eps_out: float,

@@ -63,6 +63,7 @@ class GatedMLP(FeedForward):
         self.hidden_size, self.prefix, self.intermediate_size = hidden_size, prefix, intermediate_size
         self.activation, self.biases = activation, biases
         self.gate_up = self.down = self.gate_up_bias = self.output_bias = None
+        self.fused = False
 
     def tensor_specs(self) -> list[TensorSpec]:
         p, d, i = self.prefix, self.hidden_size, self.intermediate_size
@@ -74,13 +75,23 @@ class GatedMLP(FeedForward):
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         p = self.prefix
-        self.gate_up = torch.cat([tensors[p + "gate"], tensors[p + "up"]]).contiguous()  # one product for both
+        gate, up = tensors[p + "gate"], tensors[p + "up"]
+        self.fused = gate.is_cuda and ops.swiglu_fusable(gate)
+        if self.fused:
+            # rows alternate gate_i, up_i (the biases too): the tensor-core GEMM adds the biases and
+            # applies act(gate) * up in its epilogue
+            self.gate_up = ops.interleave_gate_up(gate, up)
+        else:
+            self.gate_up = torch.cat([gate, up]).contiguous()  # one product for both, gate rows first
         self.down = tensors[p + "down"]
         if self.biases:
-            self.gate_up_bias = torch.cat([tensors[p + "gate.b"], tensors[p + "up.b"]]).contiguous()
+            b_gate, b_up = tensors[p + "gate.b"], tensors[p + "up.b"]
+            self.gate_up_bias = (torch.stack([b_gate, b_up], dim=1).reshape(-1) if self.fused else torch.cat([b_gate, b_up])).contiguous()
             self.output_bias = tensors[p + "down.b"]
 
     def inner(self, h: torch.Tensor) -> torch.Tensor:
+        if self.fused:
+            return ops.linear_glu(h, self.gate_up, self.gate_up_bias, self.activation)
         return ops.bias_glu(ops.linear(h, self.gate_up), self.gate_up_bias, self.activation)
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext) -> torch.Tensor:

@@ -149,6 +149,30 @@ def test_gated_feed_forward_alone(dtype, d, ff, T):
     check(stream, plain.rms(ref.double(), None, EPS).float(), dtype, "normed output with the bias joined in the norm's kernel")
 
 
+@pytest.mark.parametrize("activation", ["gelu_tanh", "silu", "gelu"])
+@pytest.mark.parametrize("T,d,ff,biased", [(3, 64, 40, True), (70, 2048, 96, True), (8, 4096, 1024, False), (130, 256, 200, True),
+                                           (700, 512, 1100, True), (1100, 192, 72, False)])  # fmt: skip
+def test_gated_unit_inside_the_product(activation, T, d, ff, biased):
+    """act(h gate^T + b) * (h up^T + b) from the product's own epilogue (few tokens with the weights'
+    rows on the lanes, many tokens on one SM and on pairs of them, K cut into partial sums that a
+    second kernel adds up) against float64 of the same rounded operands."""
+    from atomserve_b200 import ops
+
+    g = torch.Generator().manual_seed(T + ff)
+    gate, up = (rounded(torch.randn(ff, d, generator=g) * d**-0.5) for _ in range(2))
+    b_gate, b_up = (torch.randn(ff, generator=g) if biased else None for _ in range(2))
+    h = rounded(2 * torch.randn(T, d, generator=g))
+    zg, zu = h.double() @ gate.double().T, h.double() @ up.double().T
+    if biased:
+        zg, zu = zg + b_gate.double(), zu + b_up.double()
+    act = {"gelu_tanh": plain.gelu_tanh, "silu": plain.silu, "gelu": lambda z: 0.5 * z * (1 + torch.erf(z / math.sqrt(2.0)))}[activation]
+    w = ops.interleave_gate_up(gate.cuda().bfloat16(), up.cuda().bfloat16())
+    bias = torch.stack([b_gate, b_up], dim=1).reshape(-1).cuda().contiguous() if biased else None
+    got = ops.linear_glu(h.cuda().bfloat16(), w, bias, activation)
+    assert got.shape == (T, ff) and got.dtype == torch.bfloat16
+    check(got, (act(zg) * zu).float(), torch.bfloat16, f"{activation} unit in the epilogue")
+
+
 def paged(table, bs, positions):
     return i32([table[p // bs] * bs + p % bs for p in positions])
 
@@ -561,20 +585,31 @@ def row_errors(got, ref):
     return d.pow(2).mean(-1).sqrt() / spread
 
 
+def _toward_zero(t):
+    return (t.float().view(torch.int32) & -65536).view(torch.float32).double()
+
+
+ROUNDINGS = (lambda t: t.bfloat16().double(), _toward_zero,
+             lambda t: (t * (1 + 2.0**-9)).bfloat16().double(), lambda t: (t * (1 - 2.0**-9)).bfloat16().double())  # fmt: skip
+
+
 def allowance(cfg, w, prompt, ref):
     """What rounding alone does, per position: the error of the plain implementation itself when
-    everything an engine may keep in 16 bits is rounded to bfloat16. (The design norms every
-    sublayer's output, so single positions magnify rounding; the engine's own rounding lands on the
-    same positions, see `judge`.)"""
-    return row_errors(plain.forward(cfg, w, prompt, stored=lambda t: t.bfloat16().double()), ref)
+    everything an engine may keep in 16 bits is rounded to bfloat16. The design norms every
+    sublayer's output, so single positions magnify rounding, and which ones depends on where the
+    roundings fall: an engine that rounds other intermediate values than the plain implementation
+    (sums inside a product's epilogue, say) lands on other positions. So several ways of rounding
+    (to nearest, toward zero, to nearest after a shift of half a step up and down) each give an
+    error per position; the largest of them stands for the position."""
+    return torch.stack([row_errors(plain.forward(cfg, w, prompt, stored=f), ref) for f in ROUNDINGS]).max(0).values
 
 
 def judge(got, ref, dtype, what, lossy):
     """float32: 5e-5 of the largest logit (where a sublayer's output is small before its norm, the
     norm magnifies float32 rounding too). bfloat16: no position further off than four times what
     rounding alone does there (at least 0.1 of the spread: a wrong key, window edge or state is of
-    the order of 1), and over eight positions or more, a mean error of at most 1.5 times that of
-    rounding alone (at least 0.02)."""
+    the order of 1), and over eight positions or more, a mean error of at most that of rounding
+    alone (at least 0.02)."""
     got = got.float().cpu()
     assert got.shape == ref.shape and torch.isfinite(got).all(), what
     if dtype in ("float32", torch.float32):
@@ -585,7 +620,7 @@ def judge(got, ref, dtype, what, lossy):
     over = errors > torch.clamp(4 * lossy, min=0.1)
     assert not over.any(), f"{what}: position {int(over.nonzero()[0])} is {float(errors[over][0]):.3g} of the spread off, rounding alone {float(lossy[over][0]):.3g}"
     if len(errors) >= 8:
-        assert float(errors.mean()) <= max(0.02, 1.5 * float(lossy.mean())), f"{what}: mean error {float(errors.mean()):.3g}, rounding alone {float(lossy.mean()):.3g}"
+        assert float(errors.mean()) <= max(0.02, float(lossy.mean())), f"{what}: mean error {float(errors.mean()):.3g}, rounding alone {float(lossy.mean()):.3g}"
 
 
 @pytest.fixture(scope="module")
