@@ -14,8 +14,37 @@ __device__ __forceinline__ float glu_pair(float gate, float up, const float* __r
     up += bias[n + 1];
   }
   if (act == kGluSilu) return gate / (1.f + __expf(-gate)) * up;
-  if (act == kGluGeluTanh) return 0.5f * gate * (1.f + tanhf(0.79788456080286536f * (gate + 0.044715f * gate * gate * gate))) * up;
+  if (act == kGluGeluTanh) {
+    // 0.5 g (1 + tanh(u)) = g / (1 + exp(-2u)), u = sqrt(2 / pi) (g + 0.044715 g^3): one fast exponential, as
+    // the SiLU's; its error (a few float32 steps) is far below the rounding to bfloat16 that follows
+    const float u2 = 1.59576912160573072f * fmaf(0.044715f * gate * gate, gate, gate);
+    return gate / (1.f + __expf(-u2)) * up;
+  }
   return 0.5f * gate * (1.f + erff(gate * 0.70710678118654752f)) * up;
+}
+
+// Adds bias[n], ..., bias[n + N - 1] to N float32 sums that a thread holds as raw bits (one token's sums over N
+// neighbouring weight rows), the first `valid` of them: with all N and a 16-byte aligned start as N / 4 loads of
+// four floats, issued together (every lane of a warp reads the same addresses), else one by one.
+template <int N>
+__device__ __forceinline__ void add_bias(uint32_t (&raw)[N], const float* __restrict__ bias, int n, int valid) {
+  const float* b = bias + n;
+  if (valid >= N && (((uintptr_t)b) & 15) == 0) {
+    float4 v[N / 4];
+#pragma unroll
+    for (int j = 0; j < N / 4; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(b) + j);
+#pragma unroll
+    for (int j = 0; j < N / 4; ++j) {
+      raw[4 * j] = __float_as_uint(__uint_as_float(raw[4 * j]) + v[j].x);
+      raw[4 * j + 1] = __float_as_uint(__uint_as_float(raw[4 * j + 1]) + v[j].y);
+      raw[4 * j + 2] = __float_as_uint(__uint_as_float(raw[4 * j + 2]) + v[j].z);
+      raw[4 * j + 3] = __float_as_uint(__uint_as_float(raw[4 * j + 3]) + v[j].w);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      if (j < valid) raw[j] = __float_as_uint(__uint_as_float(raw[j]) + __ldg(b + j));
+  }
 }
 
 }  // namespace asb

@@ -42,9 +42,33 @@ struct ConvParams {
   int stride, conv_off, dt_off, C, K, H, R;
 };
 
-// grid.x: token tiles of all requests (a block finds its request by bisection), grid.y:
-// chunks of 128 columns over the C channels followed by the H step columns.
-template <typename T>
+// V neighbouring channels of one token in one load or store (V = 2 where every row's channels start at an
+// even element: half as many memory instructions, each twice as wide).
+template <typename T, int V> struct Lanes;
+template <typename T> struct Lanes<T, 1> {
+  static __device__ __forceinline__ void load(const T* at, float* v) { v[0] = asb::to_float(*at); }
+  static __device__ __forceinline__ void store(T* at, const float* v) { *at = asb::from_float<T>(v[0]); }
+};
+template <> struct Lanes<__nv_bfloat16, 2> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* at, float* v) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(at));
+    v[0] = f.x; v[1] = f.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* at, const float* v) {
+    *reinterpret_cast<__nv_bfloat162*>(at) = __floats2bfloat162_rn(v[0], v[1]);
+  }
+};
+template <> struct Lanes<float, 2> {
+  static __device__ __forceinline__ void load(const float* at, float* v) {
+    const float2 f = *reinterpret_cast<const float2*>(at);
+    v[0] = f.x; v[1] = f.y;
+  }
+  static __device__ __forceinline__ void store(float* at, const float* v) { *reinterpret_cast<float2*>(at) = make_float2(v[0], v[1]); }
+};
+
+// grid.x: token tiles of all requests (a block finds its request by bisection), grid.y: chunks of 128
+// columns: the C / V groups of V neighbouring channels, then the H step columns.
+template <typename T, int V>
 __global__ void __launch_bounds__(kConvThreads)
 conv_steps_kernel(const ConvParams p) {
   asb::pdl_wait();
@@ -61,12 +85,12 @@ conv_steps_kernel(const ConvParams p) {
   const int r = lo, row_lo = p.req_q_start[r], q_len = p.req_q_start[r + 1] - row_lo;
   const int tile = blockIdx.x - (row_lo / kConvTokens + r);
   if (tile < 0 || tile * kConvTokens >= q_len) return;
-  const int c = blockIdx.y * kConvThreads + threadIdx.x;
-  if (c >= p.C + p.H) return;
+  const int column = blockIdx.y * kConvThreads + threadIdx.x;
+  if (column >= p.C / V + p.H) return;
   const int q0 = tile * kConvTokens, nq = min(kConvTokens, q_len - q0);
   const T* proj = (const T*)p.proj;
-  if (c >= p.C) {
-    const int h = c - p.C;
+  if (column >= p.C / V) {
+    const int h = column - p.C / V;
     const float bias = p.dt_bias[h], rate = expf(p.a_log[h]);
     for (int q = q0; q < q0 + nq; ++q) {
       const size_t row = (size_t)(row_lo + q);
@@ -76,52 +100,80 @@ conv_steps_kernel(const ConvParams p) {
     }
     return;
   }
-  const int K = p.K;
-  const float* w = p.taps + (size_t)c * K;
-  const float b = p.bias[c];
+  const int K = p.K, c = column * V;
+  const float* w = p.taps + (size_t)c * K;  // channel c + v's taps: w[v * K ..]
   const float* held = p.conv_state + (size_t)p.state_slots[r] * (K - 1) * p.C + c;
   const T* in = proj + p.conv_off + c;
   T* out = (T*)p.out;
+  float b[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) b[v] = p.bias[c + v];
   if (K <= kConvWindow) {
     // Up to kConvWindow taps: the taps padded in front with zeros to kConvWindow (a zero tap leaves the
     // sum as it is, so the sum runs in the same order as below), the last kConvWindow - 1 inputs kept in
     // registers, and kConvWindow tokens at a time: their loads are in flight together, and each input
     // is read once.
-    float w8[kConvWindow], hist[kConvWindow - 1];
+    float w8[kConvWindow][V], hist[kConvWindow - 1][V];
 #pragma unroll
-    for (int j = 0; j < kConvWindow; ++j) w8[j] = j >= kConvWindow - K ? w[j - (kConvWindow - K)] : 0.f;
+    for (int j = 0; j < kConvWindow; ++j)
+#pragma unroll
+      for (int v = 0; v < V; ++v) w8[j][v] = j >= kConvWindow - K ? w[v * K + j - (kConvWindow - K)] : 0.f;
 #pragma unroll
     for (int i = 0; i < kConvWindow - 1; ++i) {
       const int at = q0 - (kConvWindow - 1) + i;  // negative: before the portion, K - 1 of them in the state
-      hist[i] = at >= 0 ? asb::to_float(in[(size_t)(row_lo + at) * p.stride]) : (K - 1 + at >= 0 ? held[(size_t)(K - 1 + at) * p.C] : 0.f);
+      if (at >= 0) {
+        Lanes<T, V>::load(in + (size_t)(row_lo + at) * p.stride, hist[i]);
+      } else if (K - 1 + at >= 0) {
+        Lanes<float, V>::load(held + (size_t)(K - 1 + at) * p.C, hist[i]);
+      } else {
+#pragma unroll
+        for (int v = 0; v < V; ++v) hist[i][v] = 0.f;
+      }
     }
     for (int q = q0; q < q0 + nq; q += kConvWindow) {
-      float x[2 * kConvWindow - 1];
+      float x[2 * kConvWindow - 1][V];
 #pragma unroll
-      for (int i = 0; i < kConvWindow - 1; ++i) x[i] = hist[i];
+      for (int i = 0; i < kConvWindow - 1; ++i)
 #pragma unroll
-      for (int i = 0; i < kConvWindow; ++i)
-        x[kConvWindow - 1 + i] = q + i < q0 + nq ? asb::to_float(in[(size_t)(row_lo + q + i) * p.stride]) : 0.f;
+        for (int v = 0; v < V; ++v) x[i][v] = hist[i][v];
 #pragma unroll
       for (int i = 0; i < kConvWindow; ++i) {
-        float acc = b;
+        if (q + i < q0 + nq) {
+          Lanes<T, V>::load(in + (size_t)(row_lo + q + i) * p.stride, x[kConvWindow - 1 + i]);
+        } else {
 #pragma unroll
-        for (int j = 0; j < kConvWindow; ++j) acc = fmaf(w8[j], x[i + j], acc);
-        if (q + i < q0 + nq) out[(size_t)(row_lo + q + i) * p.C + c] = asb::from_float<T>(silu_f(acc));
+          for (int v = 0; v < V; ++v) x[kConvWindow - 1 + i][v] = 0.f;
+        }
       }
 #pragma unroll
-      for (int i = 0; i < kConvWindow - 1; ++i) hist[i] = x[kConvWindow + i];
+      for (int i = 0; i < kConvWindow; ++i) {
+        float acc[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          acc[v] = b[v];
+#pragma unroll
+          for (int j = 0; j < kConvWindow; ++j) acc[v] = fmaf(w8[j][v], x[i + j][v], acc[v]);
+          acc[v] = silu_f(acc[v]);
+        }
+        if (q + i < q0 + nq) Lanes<T, V>::store(out + (size_t)(row_lo + q + i) * p.C + c, acc);
+      }
+#pragma unroll
+      for (int i = 0; i < kConvWindow - 1; ++i)
+#pragma unroll
+        for (int v = 0; v < V; ++v) hist[i][v] = x[kConvWindow + i][v];
     }
     return;
   }
-  for (int q = q0; q < q0 + nq; ++q) {
-    float acc = b;
-    for (int j = 0; j < K; ++j) {
-      const int at = q - (K - 1) + j;  // input index within the portion; negative: before it
-      const float v = at >= 0 ? asb::to_float(in[(size_t)(row_lo + at) * p.stride]) : held[(size_t)(K - 1 + at) * p.C];
-      acc = fmaf(w[j], v, acc);
+  for (int v = 0; v < V; ++v) {
+    for (int q = q0; q < q0 + nq; ++q) {
+      float acc = b[v];
+      for (int j = 0; j < K; ++j) {
+        const int at = q - (K - 1) + j;  // input index within the portion; negative: before it
+        const float x = at >= 0 ? asb::to_float(in[(size_t)(row_lo + at) * p.stride + v]) : held[(size_t)(K - 1 + at) * p.C + v];
+        acc = fmaf(w[v * K + j], x, acc);
+      }
+      out[(size_t)(row_lo + q) * p.C + c + v] = asb::from_float<T>(silu_f(acc));
     }
-    out[(size_t)(row_lo + q) * p.C + c] = asb::from_float<T>(silu_f(acc));
   }
 }
 
@@ -181,8 +233,17 @@ extern "C" int asb_conv_steps(void* out, float* decay, float* weight, const void
   p.out = out; p.decay = decay; p.weight = weight; p.proj = proj; p.taps = taps; p.bias = bias; p.conv_state = conv_state;
   p.dt_bias = dt_bias; p.a_log = a_log; p.state_slots = state_slots; p.req_q_start = req_q_start;
   p.stride = stride; p.conv_off = conv_off; p.dt_off = dt_off; p.C = C; p.K = K; p.H = H; p.R = R;
-  dim3 grid((num_tokens + kConvTokens - 1) / kConvTokens + R, (C + H + kConvThreads - 1) / kConvThreads);
-  ASB_DISPATCH_DTYPE(dtype, T, asb::launch(conv_steps_kernel<T>, grid, kConvThreads, 0, stream, p));
+  // two channels a thread where every row's channels start at an even element (and so at 4 or 8 bytes)
+  const int esize = dtype == asb::kFloat32 ? 4 : 2;
+  const bool two = C % 2 == 0 && conv_off % 2 == 0 && stride % 2 == 0 && K <= kConvWindow &&
+                   ((uintptr_t)proj % (2 * esize)) == 0 && ((uintptr_t)out % (2 * esize)) == 0 && ((uintptr_t)conv_state % 8) == 0;
+  const int V = two ? 2 : 1;
+  dim3 grid((num_tokens + kConvTokens - 1) / kConvTokens + R, (C / V + H + kConvThreads - 1) / kConvThreads);
+  if (two) {
+    ASB_DISPATCH_DTYPE(dtype, T, asb::launch(conv_steps_kernel<T, 2>, grid, kConvThreads, 0, stream, p));
+  } else {
+    ASB_DISPATCH_DTYPE(dtype, T, asb::launch(conv_steps_kernel<T, 1>, grid, kConvThreads, 0, stream, p));
+  }
   return asb::check_launch("conv_steps");
 }
 
