@@ -429,7 +429,9 @@ def test_latent_attention_part_alone(dtype, H, D, V, R, bs, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("C,K,H", [(160, 4, 4), (21, 1, 5), (130, 2, 3), (56, 5, 2), (448, 3, 8)])
+# (rows of even and of odd width: the kernel takes two channels a thread where it can; eight taps fill the
+# window it keeps in registers, nine and eleven take its plain loop)
+@pytest.mark.parametrize("C,K,H", [(160, 4, 4), (21, 1, 5), (130, 2, 3), (56, 5, 2), (448, 3, 8), (96, 4, 3), (40, 8, 3), (64, 9, 2), (34, 11, 3)])
 def test_convolution_steps_and_its_state(dtype, C, K, H):
     """The causal convolution per channel with bias and SiLU, reading what came before a portion from
     the request's state; the step sizes softplus(dt + bias) with decays exp(-exp(A) dt), for
@@ -570,7 +572,7 @@ def test_state_space_layer_alone(dtype, H, P, N, G, K, parts):
 
 # ---- whole models through the step function ---------------------------------------------------
 
-LENGTHS = {"a": [5, 49, 130, 1, 64], "b": [33, 2, 97, 40], "c": [300, 9, 70], "d": [20, 3, 70], "e": [45, 2, 90]}
+LENGTHS = {"a": [5, 49, 130, 1, 64], "b": [33, 2, 97, 40], "c": [300, 9, 70], "d": [20, 3, 70], "e": [45, 2, 90], "f": [150, 37, 4, 90]}
 
 
 def oracle(cfg, w, prompt):

@@ -82,5 +82,17 @@ TIGESUN_E = _model(140, 48, 1e-5, None, [attention(4, 2, 12, 20, 0.5, 30.0, 8, s
                                          attention(3, 3, 8, 8, 0.9, 300.0, 4)], repeats=[0, 0, 1])  # fmt: skip
 BLOCK_SIZE_E = 8
 
+# large heads and few of them: keys of 256 beside values of 64 and the other way round, latents of 256 and 320,
+# a state of 256 under values of 128, eight taps, a single head with a single small state
+TIGESUN_F = _model(500, 320, 1e-5, 20.0, [
+    attention(2, 1, 256, 64, 0.08, 10000.0, 128, scaling=(4.0, 512, 16.0, 1.0), ff=640),
+    latent(3, 192, 160, 256, 50, 0.07, ff=200),
+    mamba2(2, 128, 256, 1, 8, 2),
+    attention(5, 5, 32, 160, 0.2, 1e6, 32),
+    latent(2, 48, 112, 320, 129, 0.1),
+    mamba2(1, 8, 16, 1, 2, 1, ff=96),
+], repeats=[1, 2])  # fmt: skip
+BLOCK_SIZE_F = 16
+
 TIGESUN = {"a": (TIGESUN_A, BLOCK_SIZE_A), "b": (TIGESUN_B, BLOCK_SIZE_B), "c": (TIGESUN_C, BLOCK_SIZE_C),
-           "d": (TIGESUN_D, BLOCK_SIZE_D), "e": (TIGESUN_E, BLOCK_SIZE_E)}
+           "d": (TIGESUN_D, BLOCK_SIZE_D), "e": (TIGESUN_E, BLOCK_SIZE_E), "f": (TIGESUN_F, BLOCK_SIZE_F)}
