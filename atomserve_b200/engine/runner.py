@@ -280,7 +280,7 @@ class ModelRunner:
             qs[:real] = range(real)
             ss[:real] = [r.cache.state_slot for r in rows]
             for i, r in enumerate(rows):
-                if r.want:
+                for _ in r.want:  # (a place asked for twice is given twice)
                     lr[b] = i
                     b += 1
             flat = real

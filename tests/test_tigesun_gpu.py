@@ -694,6 +694,17 @@ def test_mixed_requests_reusing_pages_and_slots(models, name, dtype):
     assert len(ps3) > 4
 
 
+def test_a_place_asked_for_twice(models):
+    """A single decoded token and a portion whose wanted places name one place twice: it is given twice."""
+    cfg, bs, folder, _, ps, refs, _ = models["b"]
+    rp = replayer(folder, "float32", bs, 128)
+    p, ref = ps[0], refs[0]
+    got = rp.step([dict(id=0, tokens=p[:20], want=[19, 3, 19])], end=[])
+    judge(got, ref[[19, 3, 19]], "float32", "a portion", None)
+    got = rp.step([dict(id=0, tokens=p[20:21], want=[0, 0])], end=[0])
+    judge(got, ref[[20, 20]], "float32", "a single token", None)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(models, dtype):
     """400 tokens one by one after a short prompt: the windows pass over decoded tokens and pages
