@@ -381,9 +381,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             uint4 packed[kChunk / 16];
             __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(packed);
             if (p.glu_bias) asb::add_bias<kChunk>(raw, p.glu_bias, q0 + c, min(kChunk, p.q_rows - (q0 + c)));
-#pragma unroll
-            for (int j = 0; j < kChunk / 2; ++j)
-              ob[j] = __float2bfloat16_rn(asb::glu_pair(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1]), nullptr, 0, p.glu_act));
+            asb::glu_pairs<kChunk>(raw, ob, p.glu_act);
             if (valid == kChunk / 2 && (((uintptr_t)o) & 15) == 0) {
 #pragma unroll
               for (int v = 0; v < kChunk / 16; ++v) *reinterpret_cast<uint4*>(o + 8 * v) = packed[v];

@@ -330,9 +330,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           uint4 packed[2];
           __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(packed);
           if (p.glu_bias) asb::add_bias<32>(raw, p.glu_bias, n0 + c, valid);
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            ob[j] = __float2bfloat16_rn(asb::glu_pair(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1]), nullptr, 0, p.glu_act));
+          asb::glu_pairs<32>(raw, ob, p.glu_act);
           if (valid == 32 && (((uintptr_t)o) & 15) == 0) {
             *reinterpret_cast<uint4*>(o) = packed[0];
             *reinterpret_cast<uint4*>(o + 8) = packed[1];

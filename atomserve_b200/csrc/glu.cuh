@@ -8,19 +8,42 @@ namespace asb {
 
 enum GluAct : int { kGluSilu = 0, kGluGeluTanh = 1, kGluGelu = 2 };
 
-__device__ __forceinline__ float glu_pair(float gate, float up, const float* __restrict__ bias, int n, int act) {
-  if (bias) {
-    gate += bias[n];
-    up += bias[n + 1];
-  }
-  if (act == kGluSilu) return gate / (1.f + __expf(-gate)) * up;
-  if (act == kGluGeluTanh) {
+template <int ACT>
+__device__ __forceinline__ float glu_value(float gate, float up) {
+  if (ACT == kGluSilu) return gate / (1.f + __expf(-gate)) * up;
+  if (ACT == kGluGeluTanh) {
     // 0.5 g (1 + tanh(u)) = g / (1 + exp(-2u)), u = sqrt(2 / pi) (g + 0.044715 g^3): one fast exponential, as
     // the SiLU's; its error (a few float32 steps) is far below the rounding to bfloat16 that follows
     const float u2 = 1.59576912160573072f * fmaf(0.044715f * gate * gate, gate, gate);
     return gate / (1.f + __expf(-u2)) * up;
   }
   return 0.5f * gate * (1.f + erff(gate * 0.70710678118654752f)) * up;
+}
+
+__device__ __forceinline__ float glu_pair(float gate, float up, const float* __restrict__ bias, int n, int act) {
+  if (bias) {
+    gate += bias[n];
+    up += bias[n + 1];
+  }
+  if (act == kGluSilu) return glu_value<kGluSilu>(gate, up);
+  if (act == kGluGeluTanh) return glu_value<kGluGeluTanh>(gate, up);
+  return glu_value<kGluGelu>(gate, up);
+}
+
+// N float32 sums of one token over N neighbouring weight rows (gate, up, gate, ...; biases already added) to
+// N / 2 gated values in bfloat16: the activation is chosen once, outside the loop over the pairs.
+template <int N>
+__device__ __forceinline__ void glu_pairs(const uint32_t (&raw)[N], __nv_bfloat16* out, int act) {
+  if (act == kGluSilu) {
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) out[j] = __float2bfloat16_rn(glu_value<kGluSilu>(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1])));
+  } else if (act == kGluGeluTanh) {
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) out[j] = __float2bfloat16_rn(glu_value<kGluGeluTanh>(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1])));
+  } else {
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) out[j] = __float2bfloat16_rn(glu_value<kGluGelu>(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1])));
+  }
 }
 
 // Adds bias[n], ..., bias[n + N - 1] to N float32 sums that a thread holds as raw bits (one token's sums over N
