@@ -59,4 +59,4 @@ def config_from_dict(raw: dict) -> tuple[Architecture, Any]:
 
 def _ensure_builtin() -> None:
     if "Qwen3ForCausalLM" not in _ARCHITECTURES:
-        from atomserve_b200.models import gefilix, qwen3, tigesun, zogepel  # noqa: F401  (register themselves)
+        from atomserve_b200.models import gefilix, nipurax, qwen3, tigesun, zogepel  # noqa: F401  (register themselves)

@@ -46,6 +46,9 @@ struct AttentionParams {
   int R, H, KV, hd, bs, table_width;
   int QT, GC, HC;            // tokens per tile, heads per chunk, chunks per kv head
   int window;                // 0: none
+  int chunk;                 // 0: none; else a query sees only the keys of its own run of `chunk`
+                             // positions (runs counted from position 0 of the request)
+  float softcap;             // 0: none; else score <- softcap tanh(score / softcap)
   int PS, NP;                // partition size in keys, number of partitions (grid.z)
   float scale;
 };
@@ -85,7 +88,8 @@ paged_attention_kernel(const AttentionParams p) {
   const int num_rows = nq * gc;  // row rr = qi * gc + g
 
   // Keys this block visits.
-  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, pos0 - pos0 % p.chunk);
   const int hi = pos0 + nq;  // exclusive
   const int part = lo / p.PS + blockIdx.z;
   const int key_lo = max(lo, part * p.PS);
@@ -139,14 +143,15 @@ paged_attention_kernel(const AttentionParams p) {
       const int rr = warp + s * kWarps;
       if (rr >= num_rows) break;
       const int pq = pos0 + rr / gc;
-      const bool visible = in_range && j <= pq && (p.window <= 0 || j > pq - p.window);
+      const bool visible = in_range && j <= pq && (p.window <= 0 || j > pq - p.window) &&
+                           (p.chunk <= 0 || j >= pq - pq % p.chunk);
       float score = -INFINITY;
       if (visible) {
         const float* qrow = q_s + rr * hd;
         const float* krow = k_s + lane * kstride;
         float d = 0.f;
         for (int e = 0; e < hd; ++e) d = fmaf(qrow[e], krow[e], d);
-        score = d;
+        score = p.softcap > 0.f ? p.softcap * tanhf(d / p.softcap) : d;
       }
       const float m_new = fmaxf(m[s], asb::warp_max(score));
       if (m_new == -INFINITY) continue;  // this row sees none of these keys
@@ -359,13 +364,14 @@ extern "C" void asb_attention_tile_shape(int G, int* QT, int* GC) {
 
 // Float scratch needed when NP > 1: part_m and part_l take T*H*NP floats each, part_acc
 // T*H*NP*hd. Every partition slot of every row is written before the reduction reads it.
-extern "C" int asb_paged_attention_sink(void* out, const void* q, const void* k_cache,
-                                        const void* v_cache, const int* block_tables,
-                                        const int* req_q_start, const int* req_pos_start,
-                                        float* part_m, float* part_l, float* part_acc, const float* sink,
-                                        int num_tokens, int R, int H, int KV, int hd, int bs,
-                                        int table_width, int window, int PS, int NP, float scale,
-                                        int dtype, cudaStream_t stream) {
+// `chunk` and `softcap` (0: none): see AttentionParams.
+extern "C" int asb_paged_attention_masked(void* out, const void* q, const void* k_cache,
+                                          const void* v_cache, const int* block_tables,
+                                          const int* req_q_start, const int* req_pos_start,
+                                          float* part_m, float* part_l, float* part_acc, const float* sink,
+                                          int num_tokens, int R, int H, int KV, int hd, int bs,
+                                          int table_width, int window, int chunk, int PS, int NP, float scale,
+                                          float softcap, int dtype, cudaStream_t stream) {
   if (num_tokens == 0 || R == 0) return 0;
   if (KV < 1 || H % KV) return asb::fail("paged_attention: %d heads over %d kv heads", H, KV);
   if (hd < 1 || hd > 256) return asb::fail("paged_attention: head_dim %d not in 1..256", hd);
@@ -380,9 +386,22 @@ extern "C" int asb_paged_attention_sink(void* out, const void* q, const void* k_
   asb_attention_tile_shape(H / KV, &p.QT, &p.GC);
   p.HC = (H / KV + p.GC - 1) / p.GC;
   if (p.KV * p.HC > 65535) return asb::fail("paged_attention: too many head chunks");
-  p.window = window; p.PS = PS; p.NP = NP; p.scale = scale;
+  if (chunk < 0 || softcap < 0.f) return asb::fail("paged_attention: chunk %d and softcap %f must not be negative", chunk, (double)softcap);
+  p.window = window; p.chunk = chunk; p.softcap = softcap; p.PS = PS; p.NP = NP; p.scale = scale;
   ASB_DISPATCH_DTYPE(dtype, T, return launch<T>(p, num_tokens, stream));
   return 0;
+}
+
+extern "C" int asb_paged_attention_sink(void* out, const void* q, const void* k_cache,
+                                        const void* v_cache, const int* block_tables,
+                                        const int* req_q_start, const int* req_pos_start,
+                                        float* part_m, float* part_l, float* part_acc, const float* sink,
+                                        int num_tokens, int R, int H, int KV, int hd, int bs,
+                                        int table_width, int window, int PS, int NP, float scale,
+                                        int dtype, cudaStream_t stream) {
+  return asb_paged_attention_masked(out, q, k_cache, v_cache, block_tables, req_q_start, req_pos_start, part_m, part_l,
+                                    part_acc, sink, num_tokens, R, H, KV, hd, bs, table_width, window, 0, PS, NP, scale,
+                                    0.f, dtype, stream);
 }
 
 extern "C" int asb_paged_attention(void* out, const void* q, const void* k_cache,

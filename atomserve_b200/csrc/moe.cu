@@ -34,6 +34,7 @@ struct RouteParams {
   int* ids;        // [T, top]
   float* weights;  // [T, top]
   float* shared_gate;  // [T] or null
+  const float* bias;   // [E] or null: added to the scores for the final choice only, not to the weights
 };
 
 // one warp per token; scores and masks in shared memory
@@ -104,15 +105,20 @@ __global__ void moe_route_kernel(const RouteParams p) {
   for (int n = 0; n < p.top; ++n) {
     float best = -INFINITY;
     int at = 0x7fffffff;
-    for (int e = lane; e < p.E; e += 32)
-      if (allowed[e] > 0.f && s[e] > best) { best = s[e]; at = e; }
+    for (int e = lane; e < p.E; e += 32) {
+      const float c = p.bias ? s[e] + p.bias[e] : s[e];
+      if (allowed[e] > 0.f && c > best) { best = c; at = e; }
+    }
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
       const int oa = __shfl_xor_sync(0xffffffffu, at, o);
       if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
     if (at == 0x7fffffff) { at = 0; best = 0.f; }  // fewer allowed experts than `top`: weight 0
-    else if (lane == 0) allowed[at] = 0.f;
+    else {
+      best = s[at];  // the weight is the score itself
+      if (lane == 0) allowed[at] = 0.f;
+    }
     __syncwarp();
     sum += best;
     if ((n & 31) == lane) {
@@ -283,16 +289,23 @@ grouped_gemm_kernel(const GroupedParams p) {
 
 // ---- weighted sum back per token ----------------------------------------------------------
 
-template <typename T>
+// ids, x, experts: where ids is given, a choice of index >= experts is an identity expert, whose
+// output is the token's own input row x[t] (no row of y belongs to it).
+template <typename T, typename TX>
 __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ pair_row,
                                    const float* __restrict__ weights, const T* __restrict__ shared,
-                                   const float* __restrict__ shared_gate, int top, int N) {
+                                   const float* __restrict__ shared_gate, int top, int N,
+                                   const int* __restrict__ ids, const TX* __restrict__ x, int experts) {
   asb::pdl_wait();
   asb::pdl_launch_dependents();
   const int t = blockIdx.x;
   for (int n = threadIdx.x; n < N; n += blockDim.x) {
     float sum = 0.f;
-    for (int k = 0; k < top; ++k) sum = fmaf(weights[(size_t)t * top + k], y[(size_t)pair_row[(size_t)t * top + k] * N + n], sum);
+    for (int k = 0; k < top; ++k) {
+      const size_t pair = (size_t)t * top + k;
+      const float v = ids && ids[pair] >= experts ? asb::to_float(x[(size_t)t * N + n]) : y[(size_t)pair_row[pair] * N + n];
+      sum = fmaf(weights[pair], v, sum);
+    }
     if (shared) {
       const float sv = asb::to_float(shared[(size_t)t * N + n]);
       sum = shared_gate ? fmaf(shared_gate[t], sv, sum) : sum + sv;
@@ -305,9 +318,9 @@ int row_tiles(int pairs, int E) { return pairs / BM + (pairs < E ? pairs : E); }
 
 }  // namespace
 
-extern "C" int asb_moe_route(const float* z, int stride, int T, int E, int G, int group_top, int keep, int top,
-                             int gate_col, int softmax, int renorm, float scale, int* ids, float* weights,
-                             float* shared_gate, cudaStream_t stream) {
+extern "C" int asb_moe_route_biased(const float* z, int stride, int T, int E, int G, int group_top, int keep, int top,
+                                    int gate_col, int softmax, int renorm, float scale, const float* bias, int* ids,
+                                    float* weights, float* shared_gate, cudaStream_t stream) {
   if (T == 0) return 0;
   if (E < 1 || top < 1 || top > 32 || top > E) return asb::fail("moe_route: top %d of %d experts (at most 32)", top, E);
   if (G < 1 || E % G || keep < 1 || keep > G) return asb::fail("moe_route: %d experts in %d groups, %d kept", E, G, keep);
@@ -315,9 +328,16 @@ extern "C" int asb_moe_route(const float* z, int stride, int T, int E, int G, in
   RouteParams p;
   p.z = z; p.stride = stride; p.E = E; p.G = G; p.group_top = group_top; p.keep = keep; p.top = top;
   p.gate_col = gate_col; p.softmax = softmax; p.renorm = renorm; p.scale = scale;
-  p.ids = ids; p.weights = weights; p.shared_gate = shared_gate;
+  p.ids = ids; p.weights = weights; p.shared_gate = shared_gate; p.bias = bias;
   asb::launch(moe_route_kernel, T, 32, sizeof(float) * (2 * E + G), stream, p);
   return asb::check_launch("moe_route");
+}
+
+extern "C" int asb_moe_route(const float* z, int stride, int T, int E, int G, int group_top, int keep, int top,
+                             int gate_col, int softmax, int renorm, float scale, int* ids, float* weights,
+                             float* shared_gate, cudaStream_t stream) {
+  return asb_moe_route_biased(z, stride, T, E, G, group_top, keep, top, gate_col, softmax, renorm, scale, nullptr, ids,
+                              weights, shared_gate, stream);
 }
 
 extern "C" int asb_moe_group(const int* ids, int T, int top, int E, int* offsets, int* row_token, int* pair_row,
@@ -353,11 +373,27 @@ extern "C" int asb_moe_down(float* y, const void* hidden, const int* offsets, co
   return asb::check_launch("moe_down");
 }
 
+// ids [T, top], x [T, N] in x_dtype, experts: null / 0 for a layer without identity experts.
+extern "C" int asb_moe_combine_identity(float* out, const float* y, const int* pair_row, const float* weights,
+                                        const void* shared, const float* shared_gate, int T, int top, int N, int dtype,
+                                        const int* ids, const void* x, int x_dtype, int experts, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (ids && !x) return asb::fail("moe_combine: identity experts need the tokens' input rows");
+  const int threads = N >= 1024 ? 256 : 128;
+  ASB_DISPATCH_DTYPE(dtype, T_, {
+    if (x_dtype == asb::kFloat32)
+      asb::launch(moe_combine_kernel<T_, float>, T, threads, 0, stream, out, y, pair_row, weights, (const T_*)shared,
+                  shared_gate, top, N, ids, (const float*)x, experts);
+    else
+      asb::launch(moe_combine_kernel<T_, __nv_bfloat16>, T, threads, 0, stream, out, y, pair_row, weights,
+                  (const T_*)shared, shared_gate, top, N, ids, (const __nv_bfloat16*)x, experts);
+  });
+  return asb::check_launch("moe_combine");
+}
+
 extern "C" int asb_moe_combine(float* out, const float* y, const int* pair_row, const float* weights,
                                const void* shared, const float* shared_gate, int T, int top, int N, int dtype,
                                cudaStream_t stream) {
-  if (T == 0) return 0;
-  ASB_DISPATCH_DTYPE(dtype, T_, asb::launch(moe_combine_kernel<T_>, T, N >= 1024 ? 256 : 128, 0, stream, out, y, pair_row,
-                                            weights, (const T_*)shared, shared_gate, top, N));
-  return asb::check_launch("moe_combine");
+  return asb_moe_combine_identity(out, y, pair_row, weights, shared, shared_gate, T, top, N, dtype, nullptr, nullptr, 0, 0,
+                                  stream);
 }

@@ -127,12 +127,13 @@ class ModelRunner:
         self.block_size = cache.block_size
         # how kernels report that they could not finish (none on the CPU stand-ins of the tests)
         self.device_status = status_for(self.device) if self.device.type == "cuda" else None
-        self.views: list[CacheView | None] = [cache.entry_view(i) for i in range(len(model.schedule))]
+        # (one view per entry of the run order, and one more where the embedding keeps state)
+        self.views: list[CacheView | None] = [cache.entry_view(i) for i in range(len(model.cache_requirements()))]
         # Graphs replay the same kernels on new inputs. A part that updates state of its own in
         # place is run once more by the warm-up before a capture: where every such mixer says that
         # its state may be saved and put back around that run (`state_in_graphs`), the runner does
         # so; otherwise such models step eagerly.
-        state_ok = all(getattr(model.blocks[model.schedule[i].layer].mixer, "state_in_graphs", False) for i in cache.entry_state)
+        state_ok = all(getattr(model.state_owner(i), "state_in_graphs", False) for i in cache.entry_state)
         self.use_graphs = cuda_graphs and self.device.type == "cuda" and state_ok
         self._copy_done: torch.cuda.Event | None = None
         self._graphs = GraphCache()

@@ -17,6 +17,8 @@ from atomserve_b200.ops.experts import combine, experts_down, experts_glu, group
 from atomserve_b200.ops.latent import head_matmul, head_matmul_on_tensor_cores, latent_attention, latent_prepare
 from atomserve_b200.ops.library import KernelLibraryError, require_device
 from atomserve_b200.ops.outnorm import capped_gates_scan, gated_token_slice, head_norm_gate, projection_norm_store, residual_out_norm
+from atomserve_b200.ops.parallel_block import concat_cast, pair_embedding, residual_dual_norm
+from atomserve_b200.ops.prepare import differential_combine, qk_prepare_store
 from atomserve_b200.ops.recurrent import lightning_attention, linear_recurrence, plan_segments, rotary_table
 from atomserve_b200.ops.linear import PartialSums, interleave_gate_up, linear, linear_glu, linear_partial, linear_relu2, linear_swiglu, swiglu_fusable
 from atomserve_b200.ops.sandwich import add_normed, bias_glu, softcap_
@@ -26,6 +28,7 @@ from atomserve_b200.ops.status import DeviceStatus, status_for
 from atomserve_b200.ops.stream import activation, cast_rows, clamped_glu, embedding_scaled, gated_rms_norm, gelu, linear_for_stream, scaled_add_rms_norm
 
 __all__ = [
+    "concat_cast", "pair_embedding", "residual_dual_norm", "differential_combine", "qk_prepare_store",
     "add_normed", "bias_glu", "softcap_", "conv_state_update", "conv_steps", "gate_group_norm",
     "activation", "capped_gates_scan", "gated_token_slice", "head_norm_gate", "linear_recurrence", "projection_norm_store", "rotary_table",
     "residual_out_norm",

@@ -110,6 +110,8 @@ def paged_attention(
     host_q_lens: list[int] | None = None,
     generic: bool = False,
     sink: torch.Tensor | None = None,
+    chunk: int | None = None,
+    softcap: float | None = None,
 ) -> torch.Tensor:
     """softmax(q k^T * scale) v for every new token, keys read in place from the pages.
 
@@ -120,6 +122,10 @@ def paged_attention(
 
     `sink` (float32 [H]): a logit per query head whose exponential joins the softmax's denominator
     once; it has no key and no value and is not scaled.
+
+    `chunk`: the sequence is cut into runs of `chunk` positions, counted from position 0, and a
+    query sees only the keys of its own run (still j <= p). `softcap`: every scaled score becomes
+    softcap * tanh(score / softcap) before the softmax (the sink is not capped).
 
     bfloat16 with head size 64 or 128 runs the tensor-core kernels (decode kernel for requests
     that bring at most 8 tokens, prefill kernel for longer portions; `host_q_lens`, the tokens
@@ -137,24 +143,28 @@ def paged_attention(
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelLibraryError("paged_attention: index tensors must be contiguous int32")
     win = int(window) if window else 0
+    chunk, softcap = int(chunk or 0), float(softcap or 0.0)
     out = torch.empty_like(q)
     if sink is not None:
         require_cuda(sink)
         if sink.dtype != torch.float32 or sink.shape != (H,) or not sink.is_contiguous():
             raise KernelLibraryError(f"paged_attention: sink must be contiguous float32 [{H}]")
-    if q.dtype == torch.bfloat16 and not generic and lib().asb_attention_mma_supported(hd, H // KV):
+    # (chunks and capped scores: the general kernel)
+    masked = chunk > 0 or softcap > 0.0
+    if q.dtype == torch.bfloat16 and not generic and not masked and lib().asb_attention_mma_supported(hd, H // KV):
         return _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start,
                                     num_requests, max_context, win, scale, partitions, host_q_lens, sink)  # fmt: skip
-    ps, np_ = partitions or plan_partitions(T, num_requests, KV, H // KV, max_context, win)
+    span = min(win, chunk) if win and chunk else (win or chunk)  # a chunk bounds the keys of a row as a window does
+    ps, np_ = partitions or plan_partitions(T, num_requests, KV, H // KV, max_context, span)
     part_m = part_l = part_acc = None
     if np_ > 1:
         part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
         part_l = torch.empty_like(part_m)
         part_acc = torch.empty(T * H * np_ * hd, device=q.device, dtype=torch.float32)
-    check(lib().asb_paged_attention_sink(
+    check(lib().asb_paged_attention_masked(
         ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
         ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(sink), T, num_requests, H, KV, hd, bs,
-        block_tables.shape[1], win, ps, np_, float(scale), dtype_code(q), stream()))  # fmt: skip
+        block_tables.shape[1], win, chunk, ps, np_, float(scale), softcap, dtype_code(q), stream()))  # fmt: skip
     return out
 
 

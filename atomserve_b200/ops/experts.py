@@ -23,19 +23,22 @@ def _tensor_cores(x: torch.Tensor, *weights: torch.Tensor) -> bool:
 
 def route(z: torch.Tensor, *, experts: int, top: int, groups: int = 1, group_top: int = 2, keep: int = 1,
           scale: float = 1.0, gate_col: int | None = None, softmax: bool = False,
-          renormalise: bool = True) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:  # fmt: skip
+          renormalise: bool = True, bias: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:  # fmt: skip
     """z: float32 [T, >= experts] router logits. Returns (ids int32 [T, top], weights float32
-    [T, top], sigmoid(z[:, gate_col]) float32 [T] or None)."""
-    require_cuda(z)
+    [T, top], sigmoid(z[:, gate_col]) float32 [T] or None). `bias` (float32 [experts]) is added to
+    the scores for the final choice only; the weights are made of the scores themselves."""
+    require_cuda(z, bias)
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (experts,) or not bias.is_contiguous()):
+        raise KernelLibraryError(f"route: bias must be contiguous float32 [{experts}]")
     if z.dtype != torch.float32 or z.dim() != 2 or z.stride(1) != 1 or z.shape[1] < experts:
         raise KernelLibraryError("route: z must be float32 [tokens, >= experts] with unit column stride")
     T = z.shape[0]
     ids = torch.empty(T, top, device=z.device, dtype=torch.int32)
     weights = torch.empty(T, top, device=z.device, dtype=torch.float32)
     shared = torch.empty(T, device=z.device, dtype=torch.float32) if gate_col is not None else None
-    check(lib().asb_moe_route(ptr(z), z.stride(0), T, experts, groups, group_top, keep, top,
-                              -1 if gate_col is None else gate_col, int(softmax), int(renormalise), float(scale),
-                              ptr(ids), ptr(weights), ptr(shared), stream()))  # fmt: skip
+    check(lib().asb_moe_route_biased(ptr(z), z.stride(0), T, experts, groups, group_top, keep, top,
+                                     -1 if gate_col is None else gate_col, int(softmax), int(renormalise), float(scale),
+                                     ptr(bias), ptr(ids), ptr(weights), ptr(shared), stream()))  # fmt: skip
     return ids, weights, shared
 
 
@@ -84,14 +87,22 @@ def experts_down(hidden: torch.Tensor, offsets: torch.Tensor, down: torch.Tensor
 
 
 def combine(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None = None,
-            shared_gate: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
-    """float32 out[t] = sum_k weights[t, k] y[pair_row[t, k]] (+ shared_gate[t] * shared[t])."""
+            shared_gate: torch.Tensor | None = None, *, identity: tuple[torch.Tensor, torch.Tensor, int] | None = None) -> torch.Tensor:  # fmt: skip
+    """float32 out[t] = sum_k weights[t, k] y[pair_row[t, k]] (+ shared_gate[t] * shared[t]; without a
+    gate, + shared[t]). `identity=(ids, x, experts)`: a choice ids[t, k] >= experts is an identity
+    expert, whose output is the token's own input row x[t] instead of a row of y."""
     require_cuda(y, pair_row, weights, shared, shared_gate)
+    ids, x, experts = identity if identity is not None else (None, None, 0)
+    if identity is not None:
+        require_cuda(ids, x)
+        if ids.shape != pair_row.shape or ids.dtype != torch.int32 or x.shape != (pair_row.shape[0], y.shape[1]) or not x.is_contiguous():
+            raise KernelLibraryError("combine: identity experts need ids [tokens, top] and the input rows [tokens, width]")
     T, top = pair_row.shape
     N = y.shape[1]
     if shared is not None and (shared.shape != (T, N) or not shared.is_contiguous()):
         raise KernelLibraryError("combine: shared must be a contiguous [tokens, width] tensor")
     out = torch.empty(T, N, device=y.device, dtype=torch.float32)
-    check(lib().asb_moe_combine(ptr(out), ptr(y), ptr(pair_row), ptr(weights), ptr(shared), ptr(shared_gate), T, top, N,
-                                dtype_code(shared) if shared is not None else 0, stream()))  # fmt: skip
+    check(lib().asb_moe_combine_identity(ptr(out), ptr(y), ptr(pair_row), ptr(weights), ptr(shared), ptr(shared_gate), T, top, N,
+                                         dtype_code(shared) if shared is not None else 0, ptr(ids), ptr(x),
+                                         dtype_code(x) if x is not None else 0, int(experts), stream()))  # fmt: skip
     return out

@@ -32,6 +32,10 @@ class GQAttention(Mixer):
         scale: float | None = None,
         value_dim: int | None = None,
         names: dict[str, str] | None = None,
+        sink: bool = False,
+        softcap: float | None = None,
+        query_temperature: tuple[float, int] | None = None,
+        chunk: int | None = None,
     ):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
@@ -39,14 +43,23 @@ class GQAttention(Mixer):
         # key_dim and value_dim: the checkpoint's sizes; head_dim: what pages and kernels run at
         self.key_dim, self.value_dim = head_dim, (head_dim if value_dim is None else value_dim)
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, max(self.key_dim, self.value_dim)
-        n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight", k_norm="k_norm.weight")
+        n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight", k_norm="k_norm.weight",
+                 sink="sink")
         n.update(names or {})
         self.names = {key: prefix + value for key, value in n.items()}
         self.qk_norm_eps = qk_norm_eps
         self.window = window
         self.scale = float(scale) if scale is not None else head_dim**-0.5
         self.position = build_part("position", position, hidden_size) if position else None
-        self.qkv_proj = self.o_proj = self.q_gain = self.k_gain = None
+        # `sink`: a learned logit per head in the softmax's denominator; `softcap`: scores become
+        # softcap tanh(score / softcap); `query_temperature=(coef, every)`: queries at position p are
+        # multiplied by 1 + coef ln(floor((p + 1) / every) + 1); `chunk`: a query sees only the keys of
+        # its own run of that many positions
+        self.has_sink, self.softcap, self.chunk = bool(sink), (float(softcap) if softcap else None), chunk
+        self.query_temperature = (float(query_temperature[0]), int(query_temperature[1])) if query_temperature else None
+        if self.query_temperature is not None and (qk_norm_eps is not None or self.query_temperature[1] < 1):
+            raise ValueError("a query temperature goes with unnormed queries and a positive period")
+        self.qkv_proj = self.o_proj = self.q_gain = self.k_gain = self.sink = None
 
     def cache_spec(self) -> PageSpec:
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
@@ -64,6 +77,8 @@ class GQAttention(Mixer):
                 TensorSpec(n["q_norm"], (kd,), kind="gain", init="gain"),
                 TensorSpec(n["k_norm"], (kd,), kind="gain", init="gain"),
             ]
+        if self.has_sink:
+            specs.append(TensorSpec(n["sink"], (self.num_heads,), kind="gain", init="normal"))
         return specs
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -86,6 +101,7 @@ class GQAttention(Mixer):
             o = self.o_proj.new_zeros(self.o_proj.shape[0], self.num_heads, hd)
             o[:, :, :vd] = self.o_proj.view(-1, self.num_heads, vd)
             self.o_proj = o.view(-1, self.num_heads * hd).contiguous()
+        self.sink = tensors[n["sink"]].contiguous() if self.has_sink else None
         self.kernel_eps = self.qk_norm_eps
         if self.qk_norm_eps is not None:
             self.q_gain, self.k_gain = tensors[n["q_norm"]], tensors[n["k_norm"]]
@@ -106,9 +122,11 @@ class GQAttention(Mixer):
                 scale[: rotary.rotary_dim] = rotary.magnitude
                 self.q_gain, self.k_gain = (self.q_gain * scale).contiguous(), (self.k_gain * scale).contiguous()
 
-    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext,
+    def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext,
                 cache: CacheView | None, write_cache: bool = True) -> torch.Tensor:  # fmt: skip
-        return ops.linear(self.attend(h, ctx, cache, write_cache), self.o_proj, residual)
+        # (no residual: a block that sums in float32 itself, and the product stays float32)
+        return ops.linear(self.attend(h, ctx, cache, write_cache), self.o_proj, residual,
+                          out_dtype=torch.float32 if residual is None else None)  # fmt: skip
 
     def forward_then(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext, cache: CacheView | None,
                      write_cache: bool, then: Norm) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
@@ -132,6 +150,16 @@ class GQAttention(Mixer):
             raise NotImplementedError("this attention's fused kernel turns pairs (i, i + rotary_dim / 2) only")
         if self.position is not None and rotary is None:
             q = self._project_encode_store(h, ctx, cache, write_cache)
+        elif self.query_temperature is not None:
+            # unnormed queries scaled by position: the kernel for heads of several maps, with one map
+            # (the padded rows of the stacked weight give the zeros of the wider head size)
+            qkv = ops.linear(h, self.qkv_proj if write_cache else self.qkv_proj[: H * hd])
+            q = ops.qk_prepare_store(
+                qkv, H, KV, 1, hd, hd, hd, ctx.positions,
+                inv_freq=rotary.inv_freq if rotary else None, rotary_dim=rotary.rotary_dim if rotary else 0,
+                temperature=self.query_temperature, slots=cache.slots if write_cache else None,
+                k_cache=cache.k if write_cache else None, v_cache=cache.v if write_cache else None,
+            )  # fmt: skip
         else:
             # reading another entry's keys and values, only queries are projected
             weight, kv_heads = (self.qkv_proj, KV) if write_cache else (self.qkv_proj[: H * hd], 0)
@@ -151,7 +179,7 @@ class GQAttention(Mixer):
         out = ops.paged_attention(
             q, cache.k, cache.v, cache.block_tables, ctx.req_q_start, ctx.req_pos_start,
             num_requests=ctx.num_requests, max_context=ctx.max_context, window=self.window,
-            scale=self.scale, host_q_lens=ctx.host_q_lens or None,
+            scale=self.scale, host_q_lens=ctx.host_q_lens or None, sink=self.sink, chunk=self.chunk, softcap=self.softcap,
         )  # fmt: skip
         return out.view(-1, H * hd)
 

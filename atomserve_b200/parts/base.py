@@ -225,6 +225,18 @@ class TokenInput(Part):
         raise NotImplementedError
 
 
+class StreamStep(Part):
+    """A transformation of the residual stream between two layers of the run order:
+    forward(x, x0, number, ctx) -> x, with x0 what the embedding gave for the step's tokens and
+    `number` the count the run order attaches to this use (which pass of a loop it opens)."""
+
+    def bind_dtype(self, dtype: torch.dtype) -> None:
+        pass
+
+    def forward(self, x: torch.Tensor, x0: torch.Tensor, number: int, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
@@ -268,6 +280,7 @@ class Block(Part):
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
     "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "embedding": {}, "head": {}, "token_input": {},
+    "stream_step": {},
 }  # fmt: skip
 
 
@@ -300,6 +313,6 @@ def build_block(kind: str, mixer: Mixer, feed_forward: FeedForward, mixer_norm: 
 def _ensure_builtin() -> None:
     if "rms_norm" not in _REGISTRIES["norm"]:
         from atomserve_b200.parts import (  # noqa: F401
-            attention, block, embedding, experts, latent_attention, lightning, matrix_memory, mlp, norms, parallel, rotary,
-            sink_attention, state_space, token_input,
+            attention, block, differential_attention, embedding, experts, latent_attention, lightning, matrix_memory, mlp,
+            norms, parallel, rotary, sink_attention, state_space, stream_step, token_input,
         )

@@ -128,6 +128,44 @@ class SandwichNormBlock(PostNormBlock):
         return self.feed_forward_norm.add_forward(x, y, then, getattr(self.feed_forward, "output_bias", None))
 
 
+class ParallelResidualBlock(PostNormBlock):
+    """The arrangement in which mixer and feed-forward read the same float32 stream, each through
+    an RMS norm of its own, and are added together: x <- x + mult (mixer(N1 x) + ff(N2 x)); a layer
+    without a feed-forward adds the mixer alone. The norms are `RMSNorm`s; `mult` is the mixer
+    norm's `mult` (`ScaledRMSNorm`), 1 without one. The kernel that adds a layer's two outputs also
+    norms the sum twice for the next block of this kind, so the pair (N1 x, N2 x) travels from
+    block to block in the place where pre-norm blocks hand on their normed input. Sublayers give
+    float32 outputs (`forward_for_stream` must not leave partial sums: two products are added)."""
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        super().load(tensors)
+        self.mult = float(getattr(self.mixer_norm, "mult", 1.0))
+
+    def norms(self) -> tuple[torch.Tensor, torch.Tensor | None, float]:
+        return self.mixer_norm.gain, (self.feed_forward_norm.gain if self.has_feed_forward else None), self.mixer_norm.eps
+
+    def forward_chain(self, x: torch.Tensor, normed, ctx: StepContext, cache: CacheView | None,
+                      write_cache: bool, then: Norm | None) -> tuple[torch.Tensor, object]:  # fmt: skip
+        g1, g2, eps = self.norms()
+        if normed is None:
+            _, h1, h2 = ops.residual_dual_norm(x, None, None, 1.0, g1, g2, eps, self.dtype, want_stream=False)
+        else:
+            h1, h2 = normed
+        y1 = self.mixer.forward(h1, None, ctx, cache, write_cache)
+        y2 = self.feed_forward.forward(h2, None, ctx) if self.has_feed_forward else None
+        owner = getattr(then, "block_norms", None) if then is not None else None
+        if owner is None:  # the last block, or one of another kind next: the sum alone
+            return ops.residual_dual_norm(x, y1, y2, self.mult, None, None, 0.0, self.dtype)[0], None
+        n1, n2, eps_next = owner()
+        x, h1, h2 = ops.residual_dual_norm(x, y1, y2, self.mult, n1, n2, eps_next, self.dtype)
+        return x, (h1, h2)
+
+    def bind_dtype(self, dtype: torch.dtype) -> None:
+        super().bind_dtype(dtype)
+        self.mixer_norm.block_norms = self.norms  # how the block before this one learns both gains
+
+
+register_part("block", "parallel_residual", ParallelResidualBlock)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "output_norm", OutputNormBlock)

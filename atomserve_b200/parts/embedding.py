@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from atomserve_b200 import ops
-from atomserve_b200.parts.base import Part, register_part
+from atomserve_b200.parts.base import CacheView, Part, StateSpec, StepContext, register_part
 from atomserve_b200.parts.spec import TensorSpec
 
 
@@ -64,6 +64,44 @@ class NormedEmbedding(TokenEmbedding):
         return ops.scaled_add_rms_norm(rows, None, 1.0, self.gain, self.eps, torch.float32)[0]
 
 
+class PairHashEmbedding(TokenEmbedding):
+    """table[token] + pairs[(previous token * mul_prev + token * mul_cur) mod buckets] as float32:
+    a hashed table of token pairs beside the token table. `pairs` has buckets + 1 rows; the last
+    one serves a sequence's first token, which has no predecessor. The token before a step's first
+    one is kept per request as state (`last`: that id plus one, 0 after admission), so prompts may
+    be cut anywhere and decoded tokens know their predecessor without the host's help."""
+
+    state_in_graphs = True  # one int per request, saved and put back around a capture's warm-up run
+
+    def __init__(self, hidden_size: int, prefix: str, vocab_size: int, buckets: int, mul_prev: int, mul_cur: int,
+                 tensor: str | None = None, pair_tensor: str | None = None):  # fmt: skip
+        super().__init__(hidden_size, prefix, vocab_size, tensor)
+        if buckets < 1:
+            raise ValueError(f"a pair table needs at least one bucket, got {buckets}")
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.pair_name = pair_tensor or prefix + "pairs"
+        self.pairs: torch.Tensor | None = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return super().tensor_specs() + [TensorSpec(self.pair_name, (self.buckets + 1, self.hidden_size))]
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        super().load(tensors)
+        self.pairs = tensors[self.pair_name]
+
+    def state_specs(self) -> list[StateSpec]:
+        return [StateSpec("last", (1,), torch.int32)]
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise RuntimeError("a pair embedding needs the step's requests and their state: forward_step(ctx, cache)")
+
+    def forward_step(self, ctx: StepContext, cache: CacheView | None) -> torch.Tensor:
+        if cache is None or "last" not in cache.state:
+            raise RuntimeError("a pair embedding needs its per-request state")
+        return ops.pair_embedding(ctx.token_ids, ctx.positions, ctx.req_q_start, ctx.state_slots, cache.state["last"],
+                                  self.table, self.pairs, self.mul_prev, self.mul_cur, self.status)  # fmt: skip
+
+
 class LMHead(Part):
     """`softcap`: logits <- softcap tanh(logits / softcap), on the float32 logits."""
 
@@ -91,4 +129,5 @@ class LMHead(Part):
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "scaled_embedding", ScaledEmbedding)
 register_part("embedding", "normed_embedding", NormedEmbedding)
+register_part("embedding", "pair_hash_embedding", PairHashEmbedding)
 register_part("head", "lm_head", LMHead)

@@ -61,8 +61,15 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, prefix: str, experts: int, top: int, expert_ff: int, limit: float = 0.0,
                  groups: int = 1, group_top: int = 2, keep: int = 1, scale: float = 1.0, slope: float = 1.0,
                  shift: float = 0.0, score: str = "sigmoid", renormalise: bool = True, shared_ff: int | None = None,
-                 shared_limit: float | None = None, shared_gated: bool = True):  # fmt: skip
-        if experts % groups or not 1 <= keep <= groups or not 1 <= top <= experts // groups * keep:
+                 shared_limit: float | None = None, shared_gated: bool = True, identity: int = 0,
+                 choice_offsets: bool = False):  # fmt: skip
+        # `identity`: that many further router outputs are experts without tensors whose output is their
+        # input; `choice_offsets`: a learned vector (`correction`) joins the scores when the experts are
+        # chosen and stays out of their weights
+        self.identity, self.choice_offsets = int(identity), bool(choice_offsets)
+        if self.identity and groups != 1:
+            raise ValueError("identity experts belong to no group of experts")
+        if experts % groups or not 1 <= keep <= groups or not 1 <= top <= (experts + self.identity) // groups * keep:
             raise ValueError(f"{experts} experts in {groups} groups, {keep} kept, cannot give {top} choices")
         if score not in ("sigmoid", "softmax"):
             raise ValueError(f"score {score!r} is neither 'sigmoid' nor 'softmax'")
@@ -79,7 +86,9 @@ class RoutedExperts(FeedForward):
         specs = []
         for e in range(self.experts):
             specs += [TensorSpec(f"{p}e{e}.gate", (f, d)), TensorSpec(f"{p}e{e}.up", (f, d)), TensorSpec(f"{p}e{e}.down", (d, f))]
-        specs.append(TensorSpec(p + "router", (self.experts, d)))
+        specs.append(TensorSpec(p + "router", (self.experts + self.identity, d)))
+        if self.choice_offsets:
+            specs.append(TensorSpec(p + "correction", (self.experts + self.identity,), kind="gain", init="normal"))
         if self.shared_ff is not None:
             s = self.shared_ff
             specs += [TensorSpec(p + "shared.gate", (s, d)), TensorSpec(p + "shared.up", (s, d)), TensorSpec(p + "shared.down", (d, s))]
@@ -99,22 +108,25 @@ class RoutedExperts(FeedForward):
             self.shared_gate_up = torch.cat([tensors[p + "shared.gate"], tensors[p + "shared.up"]]).contiguous()
             self.shared_down = tensors[p + "shared.down"]
         self.router = torch.cat(rows).contiguous()
+        self.offsets = tensors[p + "correction"].contiguous() if self.choice_offsets else None
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor | None, ctx: StepContext) -> torch.Tensor:
-        E = self.experts
+        E, routed = self.experts, self.experts + self.identity
         z = ops.linear(h, self.router, out_dtype=torch.float32)
         ids, weights, shared_gate = ops.route(
-            z, experts=E, top=self.top, groups=self.groups, group_top=self.group_top, keep=self.keep, scale=self.scale,
-            gate_col=E if self.shared_gated else None, softmax=self.score == "softmax", renormalise=self.renormalise,
+            z, experts=routed, top=self.top, groups=self.groups, group_top=self.group_top, keep=self.keep, scale=self.scale,
+            gate_col=routed if self.shared_gated else None, softmax=self.score == "softmax", renormalise=self.renormalise,
+            bias=self.offsets,
         )  # fmt: skip
-        offsets, row_token, pair_row = ops.group_by_expert(ids, E)
+        # (the identity experts' pairs are sorted behind the last expert's rows, where no product looks)
+        offsets, row_token, pair_row = ops.group_by_expert(ids, routed)
         hidden = ops.experts_glu(h, row_token, offsets, self.gate, self.up, self.limit, self.slope, self.shift)
         y = ops.experts_down(hidden, offsets, self.down)
         shared = None
         if self.shared_ff is not None:
             inner = ops.clamped_glu(ops.linear(h, self.shared_gate_up), self.shared_limit, self.slope, self.shift)
-            shared = ops.linear(inner, self.shared_down)
-        out = ops.combine(y, pair_row, weights, shared, shared_gate)
+            shared = ops.linear(inner, self.shared_down, out_dtype=torch.float32 if residual is None else None)
+        out = ops.combine(y, pair_row, weights, shared, shared_gate, identity=(ids, h, E) if self.identity else None)
         if residual is None:
             return out
         return residual + out.to(residual.dtype)

@@ -31,8 +31,11 @@ class DecoderModel:
                 if not hasattr(block, "attach"):
                     raise ValueError(f"a {layer.block!r} block takes no token input")
                 block.attach(build_part("token_input", layer.token_input, d))
+        self.stream_steps = [build_part("stream_step", step, d) for step in spec.stream_steps]
         self.schedule = spec.schedule
         for i, call in enumerate(self.schedule):
+            if call.before is not None and not 0 <= call.before[0] < len(self.stream_steps):
+                raise ValueError(f"run order entry {i} names stream step {call.before[0]} of {len(self.stream_steps)}")
             if not 0 <= call.layer < len(self.blocks):
                 raise ValueError(f"run order entry {i} names layer {call.layer} of {len(self.blocks)}")
             if call.cache_from is not None:
@@ -45,7 +48,7 @@ class DecoderModel:
         self.device: torch.device | None = None
 
     def parts(self):
-        return [self.embedding, *self.blocks, self.final_norm, self.head]
+        return [self.embedding, *self.stream_steps, *self.blocks, self.final_norm, self.head]
 
     def tensor_specs(self) -> list[TensorSpec]:
         seen: dict[str, TensorSpec] = {}
@@ -68,9 +71,14 @@ class DecoderModel:
             if bind is not None:
                 bind(self.dtype)
 
+    def state_owner(self, entry: int):
+        """The part whose state lives under `entry` of `cache_requirements`."""
+        return self.blocks[self.schedule[entry].layer].mixer if entry < len(self.schedule) else self.embedding
+
     def cache_requirements(self) -> list[tuple[PageSpec | None, list[StateSpec]]]:
         """For each entry of the run order: the pages and state it owns (none if it reads
-        another entry's)."""
+        another entry's). An embedding that keeps state of its own per request (`state_specs`) has
+        one more entry behind them, number len(schedule)."""
         out = []
         for call in self.schedule:
             mixer = self.blocks[call.layer].mixer
@@ -78,17 +86,31 @@ class DecoderModel:
                 out.append((None, []))
             else:
                 out.append((mixer.cache_spec(), mixer.state_specs()))
+        kept = getattr(self.embedding, "state_specs", None)
+        if kept is not None and kept():
+            out.append((None, kept()))
         return out
 
     def forward(self, ctx: StepContext, views: list[CacheView | None], logits_out: torch.Tensor | None = None) -> torch.Tensor:
         """Run the T tokens of the step; float32 logits [len(ctx.logits_rows), vocab], written
         into `logits_out` where the caller brings the buffer (a head whose `forward` takes no
         `out` has its result copied there)."""
-        x = self.embedding.forward(ctx.token_ids)
+        if hasattr(self.embedding, "forward_step"):  # an embedding that reads more of the step than its token ids
+            x = self.embedding.forward_step(ctx, views[len(self.schedule)] if len(views) > len(self.schedule) else None)
+        else:
+            x = self.embedding.forward(ctx.token_ids)
+        x0 = x
         normed = None  # the next block's first norm of x, where the block before it has computed it
         for i, call in enumerate(self.schedule):
             own = call.cache_from is None
-            then = self.blocks[self.schedule[i + 1].layer].mixer_norm if i + 1 < len(self.schedule) else None
+            if call.before is not None:
+                step = self.stream_steps[call.before[0]]
+                if hasattr(step, "forward_then"):  # a step that can also norm its result for the block it opens
+                    x, normed = step.forward_then(x, x0, call.before[1], ctx, self.blocks[call.layer].mixer_norm)
+                else:
+                    x, normed = step.forward(x, x0, call.before[1], ctx), None
+            last = i + 1 == len(self.schedule) or self.schedule[i + 1].before is not None  # (a stream step norms nothing)
+            then = None if last else self.blocks[self.schedule[i + 1].layer].mixer_norm
             x, normed = self.blocks[call.layer].forward_chain(
                 x, normed, ctx, views[i if own else call.cache_from], own, then
             )

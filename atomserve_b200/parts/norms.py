@@ -39,6 +39,16 @@ class RMSNorm(Norm):
         return total, self.forward(total)
 
 
+class ScaledRMSNorm(RMSNorm):
+    """An RMS norm that also carries `mult`, the factor by which its block multiplies what the
+    sublayers give before adding it to the stream (blocks that sum their sublayers themselves)."""
+
+    def __init__(self, hidden_size: int, prefix: str, eps: float, mult: float = 1.0, width: int | None = None,
+                 tensor: str | None = None):  # fmt: skip
+        super().__init__(hidden_size, prefix, eps, width, tensor)
+        self.mult = float(mult)
+
+
 class StreamRMSNorm(RMSNorm):
     """RMSNorm of a residual stream that is kept in float32 whatever the compute dtype, for
     blocks whose norm follows the sum: `add_forward(x, y)` is norm(alpha x + y), returned both as
@@ -144,6 +154,7 @@ class NoNorm(Norm):
 
 
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "scaled_rms_norm", ScaledRMSNorm)
 register_part("norm", "stream_rms_norm", StreamRMSNorm)
 register_part("norm", "output_norm", OutputNorm)
 register_part("norm", "sandwich_norm", SandwichNorm)

@@ -79,5 +79,32 @@ class ScaledRotary(Rotary):
         raise NotImplementedError("the stand-alone rotary kernel has no magnitude; mixers apply this encoding fused")
 
 
+class BandScaledRotary(Rotary):
+    """Rotary encoding whose slow frequencies are divided by `factor` for contexts longer than the
+    `original` one, chosen by wavelength l_i = 2 pi / f_i: a wave shorter than original / high
+    keeps f_i, one longer than original / low turns at f_i / factor, and between the two the
+    frequencies are mixed, (1 - s) f_i / factor + s f_i with s = (original / l_i - low) /
+    (high - low). Cosines and sines keep their size. The table is made once, in float64."""
+
+    def __init__(self, hidden_size: int, prefix: str, head_dim: int, theta: float, factor: float, original: float,
+                 low: float, high: float, rotary_dim: int | None = None, pairing: str = "half"):  # fmt: skip
+        super().__init__(hidden_size, prefix, head_dim, theta, rotary_dim, pairing)
+        if not factor > 0 or not original > 0 or not high > low >= 0:
+            raise ValueError("a band-scaled rotary encoding needs factor > 0, original > 0 and high > low >= 0")
+        self.factor, self.original, self.low, self.high = float(factor), float(original), float(low), float(high)
+
+    def prepare(self, device: torch.device) -> None:
+        dims = self.rotary_dim
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = self.theta ** (-2.0 * i / dims) if dims else i
+        if dims:
+            turns = self.original * f / (2.0 * math.pi)  # original / wavelength
+            mix = torch.clamp((turns - self.low) / (self.high - self.low), 0.0, 1.0)
+            mixed = (1.0 - mix) * f / self.factor + mix * f
+            f = torch.where(turns > self.high, f, torch.where(turns < self.low, f / self.factor, mixed))
+        self.inv_freq = f.to(torch.float32).to(device)
+
+
+register_part("position", "band_scaled_rotary", BandScaledRotary)
 register_part("position", "rotary", Rotary)
 register_part("position", "scaled_rotary", ScaledRotary)

@@ -56,10 +56,13 @@ class LayerSpec:
 class LayerCall:
     """One entry of the run order. `layer` indexes ModelSpec.layers (the same layer may be
     called twice: shared weights, separate caches). `cache_from`, if set, is the index of an
-    earlier entry of the run order whose cache this call reads instead of owning one."""
+    earlier entry of the run order whose cache this call reads instead of owning one. `before`,
+    if set, is (index into ModelSpec.stream_steps, pass number): that step transforms the stream
+    right before this call (the opening of a pass of a loop over layers, say)."""
 
     layer: int
     cache_from: int | None = None
+    before: tuple[int, int] | None = None
 
 
 @dataclass(frozen=True)
@@ -74,3 +77,5 @@ class ModelSpec:
     head: PartSpec
     # checkpoint names that may be present and are ignored (a tied model shipping a head copy)
     ignored_tensors: tuple[str, ...] = ()
+    # parts of the "stream_step" family that run orders may place before a layer (`LayerCall.before`)
+    stream_steps: tuple[PartSpec, ...] = ()
