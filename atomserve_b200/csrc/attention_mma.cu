@@ -45,11 +45,18 @@ struct MmaParams {
   int G, GC, HC;             // heads per kv head, heads per block (<= 16), chunks per kv head
   int QT;                    // prefill: tokens per 128-row tile
   int window, PS, NP;
+  int chunk;                 // 0: none; else a query sees only the keys of its own run of `chunk` positions
+  float softcap;             // 0: none; else score <- softcap tanh(score / softcap)
   int all_single;            // every request brings exactly one token: request = row
   int short_rows;            // > 0: the decode kernel's grid and the partial results count only the rows of
                              // requests with at most kShortRows tokens (a step that also holds longer portions)
   float scale;
 };
+
+// cap * tanh(x / cap) through one exponential: tanh(y) = 1 - 2 / (exp(2y) + 1); exact limits at both ends
+__device__ __forceinline__ float capped(float x, float cap) {
+  return cap * (1.f - __fdividef(2.f, __expf(2.f * x / cap) + 1.f));
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -304,7 +311,8 @@ decode_attention_kernel(const MmaParams p) {
   const int head0 = kvh * p.G + (blockIdx.y % p.HC) * p.GC;
   const int gc = min(p.GC, kvh * p.G + p.G - head0);
 
-  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
   const int part = lo / p.PS + blockIdx.z;
   const int key_lo = max(lo, part * p.PS);
   const int key_hi = (int)min((long long)pos + 1, (long long)(part + 1) * p.PS);
@@ -357,6 +365,7 @@ decode_attention_kernel(const MmaParams p) {
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
+          if (p.softcap > 0.f) s[j][e] = capped(s[j][e], p.softcap);
           const int key = kt0 + key0 + j * 8 + (lane & 3) * 2 + (e & 1);
           if (key < key_lo || key >= key_hi) s[j][e] = -INFINITY;
         }
@@ -508,7 +517,8 @@ prefill_attention_kernel(const MmaParams p) {
   const int num_rows = nq * gc;  // tile row rr = qi * gc + g
   const int* table = p.block_tables + (size_t)r * p.table_width;
 
-  const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  if (p.chunk > 0) key_lo = max(key_lo, pos0 - pos0 % p.chunk);
   const int key_hi = pos0 + nq;
 
   {
@@ -544,9 +554,13 @@ prefill_attention_kernel(const MmaParams p) {
   // keys this warp's rows can see at all
   const int warp_first = warp * 16, warp_last = min(warp * 16 + 15, num_rows - 1);
   const int warp_hi = warp_first < num_rows ? pos0 + warp_last / gc + 1 : 0;
-  const int warp_lo = p.window > 0 ? max(0, pos0 + warp_first / gc - p.window + 1) : 0;
   const int warp_min_pos = pos0 + warp_first / gc;            // position of the warp's first row
   const int warp_max_pos = warp_hi - 1;                       // and of its last real row
+  int warp_lo = p.window > 0 ? max(0, warp_min_pos - p.window + 1) : 0;
+  if (p.chunk > 0) warp_lo = max(warp_lo, warp_min_pos - warp_min_pos % p.chunk);
+  // where the last row's run of positions begins: tiles from there on lie in every row's run
+  const int warp_chunk_lo = p.chunk > 0 && warp_max_pos >= 0 ? warp_max_pos - warp_max_pos % p.chunk : 0;
+  const float cap2 = p.softcap * 1.4426950408889634f;         // the cap in the scores' log2 units
   const bool warp_full = warp_first + 15 < num_rows;          // no padding rows in this warp
 
   const int kt_begin = (key_lo / kKeyTile) * kKeyTile;
@@ -593,16 +607,19 @@ prefill_attention_kernel(const MmaParams p) {
       // Masks are needed only where the tile touches a row's own position, the window's edge or
       // the ends of the key range; tiles strictly inside every row's view skip them.
       const bool inside = warp_full && kt0 + kKeyTile <= warp_min_pos + 1 && kt0 >= key_lo && kt0 + kKeyTile <= key_hi &&
-                          (p.window <= 0 || kt0 > warp_max_pos - p.window);
+                          (p.window <= 0 || kt0 > warp_max_pos - p.window) && kt0 >= warp_chunk_lo;
       float rmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int j = 0; j < kKeyTile / 8; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
+          // (a group no row sees holds -inf, which the cap turns into -cap: such tiles are never `inside`)
+          if (cap2 > 0.f) s[j][e] = capped(s[j][e], cap2);
           if (!inside) {
             const int key = kt0 + j * 8 + (lane & 3) * 2 + (e & 1);
             const int qp = qpos[e >> 1];
-            const bool visible = key <= qp && key >= key_lo && (p.window <= 0 || key > qp - p.window);
+            const bool visible = key <= qp && key >= key_lo && (p.window <= 0 || key > qp - p.window) &&
+                                 (p.chunk <= 0 || key >= qp - qp % p.chunk);
             if (!visible) s[j][e] = -INFINITY;
           }
           rmax[e >> 1] = fmaxf(rmax[e >> 1], s[j][e]);
@@ -730,14 +747,16 @@ extern "C" int asb_attention_mma_supported(int hd, int group) {
 // short_rows > 0 (with run_decode alone): the number of rows of requests with at most 8 tokens in
 // a step that also holds longer portions; the decode kernel then starts blocks for those rows
 // only, and the scratch is [short_rows, H, NP(, hd)], merged by asb_attention_reduce_short.
-extern "C" int asb_paged_attention_mma_sink(void* out, const void* q, const void* k_cache,
-                                            const void* v_cache, const int* block_tables,
-                                            const int* req_q_start, const int* req_pos_start,
-                                            float* part_m, float* part_l, float* part_acc, const float* sink,
-                                            int num_tokens, int R, int H, int KV, int hd, int bs,
-                                       int table_width, int window, int PS, int NP, float scale,
-                                       int run_decode, int run_prefill, int all_single, int short_rows,
-                                       cudaStream_t stream) {
+// chunk, softcap (0: none): see MmaParams.
+extern "C" int asb_paged_attention_mma_masked(void* out, const void* q, const void* k_cache,
+                                              const void* v_cache, const int* block_tables,
+                                              const int* req_q_start, const int* req_pos_start,
+                                              float* part_m, float* part_l, float* part_acc, const float* sink,
+                                              int num_tokens, int R, int H, int KV, int hd, int bs,
+                                              int table_width, int window, int chunk, int PS, int NP, float scale,
+                                              float softcap, int run_decode, int run_prefill, int all_single,
+                                              int short_rows, cudaStream_t stream) {
+  if (chunk < 0 || softcap < 0.f) return asb::fail("paged_attention_mma: chunk %d and softcap %f must not be negative", chunk, (double)softcap);
   if (num_tokens == 0 || R == 0) return 0;
   if (short_rows < 0 || short_rows > num_tokens || (short_rows > 0 && (run_prefill || all_single)))
     return asb::fail("paged_attention_mma: %d short rows of %d tokens (decode-only launches of mixed steps)", short_rows, num_tokens);
@@ -759,8 +778,22 @@ extern "C" int asb_paged_attention_mma_sink(void* out, const void* q, const void
   p.QT = kPrefillRows / p.GC;
   if (p.KV * p.HC > 65535) return asb::fail("paged_attention_mma: too many head chunks");
   p.window = window; p.PS = PS; p.NP = NP; p.all_single = all_single; p.short_rows = short_rows; p.scale = scale;
+  p.chunk = chunk; p.softcap = softcap;
   if (hd == 64) return launch_mma<64>(p, run_decode, run_prefill, stream);
   return launch_mma<128>(p, run_decode, run_prefill, stream);
+}
+
+extern "C" int asb_paged_attention_mma_sink(void* out, const void* q, const void* k_cache,
+                                            const void* v_cache, const int* block_tables,
+                                            const int* req_q_start, const int* req_pos_start,
+                                            float* part_m, float* part_l, float* part_acc, const float* sink,
+                                            int num_tokens, int R, int H, int KV, int hd, int bs,
+                                            int table_width, int window, int PS, int NP, float scale,
+                                            int run_decode, int run_prefill, int all_single, int short_rows,
+                                            cudaStream_t stream) {
+  return asb_paged_attention_mma_masked(out, q, k_cache, v_cache, block_tables, req_q_start, req_pos_start, part_m,
+                                        part_l, part_acc, sink, num_tokens, R, H, KV, hd, bs, table_width, window, 0, PS,
+                                        NP, scale, 0.f, run_decode, run_prefill, all_single, short_rows, stream);
 }
 
 extern "C" int asb_paged_attention_mma(void* out, const void* q, const void* k_cache,

@@ -67,7 +67,10 @@ struct AttnParams {
   int T, R, H, KV, bs, table_width;
   int G, QT;                 // query heads per kv head, tokens per tile (128 / G)
   int window;
+  int chunk;                 // 0: none; else a query sees only the keys of its own run of `chunk` positions
   float scale_log2;          // softmax scale times log2(e)
+  float cap_log2;            // 0: none; else softcap times log2(e): score <- softcap tanh(score / softcap)
+  float scale_over_cap;      // 2 log2(e) scale / softcap: the exponent of the tanh's one exponential
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -128,7 +131,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int kvh = blockIdx.x % p.KV;
   const int head0 = kvh * p.G;
   const int* table = p.block_tables + (size_t)r * p.table_width;
-  const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  if (p.chunk > 0) key_lo = max(key_lo, pos0 - pos0 % p.chunk);
   const int key_hi = pos0 + nq;  // exclusive
   const int kt_begin = (key_lo / kKeys) * kKeys;
   const int num_tiles = (key_hi - kt_begin + kKeys - 1) / kKeys;
@@ -275,7 +279,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int qi = row / p.G;
     const bool real = qi < nq;
     const int pos = real ? pos0 + qi : -1;  // padding rows see nothing
-    const int row_lo = p.window > 0 ? max(key_lo, pos - p.window + 1) : key_lo;
+    int row_lo = p.window > 0 ? max(key_lo, pos - p.window + 1) : key_lo;
+    if (p.chunk > 0 && pos >= 0) row_lo = max(row_lo, pos - pos % p.chunk);
+    // where the last row's run of positions begins: tiles from there on lie in every row's run
+    const int chunk_lo = p.chunk > 0 ? (pos0 + nq - 1) - (pos0 + nq - 1) % p.chunk : 0;
+    // capped scores are kept in log2 units already: nothing is left to multiply them by
+    const float mul = p.cap_log2 > 0.f ? 1.f : p.scale_log2;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const bool real_block = nq * p.G == kRows;  // no padding rows in this block
     float m = -INFINITY, l = 0.f;
@@ -294,11 +303,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // and kept in registers. Tiles strictly inside every row's view (below the diagonal,
       // inside the window) need no mask.
       const bool inside = kt0 + kKeys <= pos0 + 1 && kt0 >= key_lo && real_block &&
-                          (p.window <= 0 || kt0 > pos0 + nq - 1 - p.window);
+                          (p.window <= 0 || kt0 > pos0 + nq - 1 - p.window) && kt0 >= chunk_lo;
       uint32_t raw[kKeys];
 #pragma unroll
       for (int c = 0; c < kKeys; c += 32) tmem_ld32_nowait(tmem_s(j) + lane_addr + (uint32_t)c, raw + c);
       tmem_ld_wait();
+      if (p.cap_log2 > 0.f) {
+        // cap tanh(score / cap) through one exponential, tanh(y) = 1 - 2 / (exp(2y) + 1)
+#pragma unroll
+        for (int i = 0; i < kKeys; ++i) {
+          const float t = fast_exp2(__uint_as_float(raw[i]) * p.scale_over_cap);
+          raw[i] = __float_as_uint(p.cap_log2 * (1.f - __fdividef(2.f, t + 1.f)));
+        }
+      }
       // (eight running maxima, so that no comparison waits for the one before it)
       float part_max[8];
 #pragma unroll
@@ -316,7 +333,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       const float raw_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
                                   fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
-      const float tile_max = raw_max * p.scale_log2;  // the scale is positive
+      const float tile_max = raw_max * mul;  // the scale is positive
       // The running maximum moves only when the new one exceeds it by more than 8 (a factor of
       // 256 in the probabilities, harmless in float32 sums and bfloat16 operands); otherwise the
       // older maximum stays and neither the sum nor the accumulator needs rescaling.
@@ -354,8 +371,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       float part_sum[4] = {0.f, 0.f, 0.f, 0.f};  // the tile's sum in four strands, added to the row's at the end
 #pragma unroll
       for (int i = 0; i < kKeys; i += 2) {
-        const float a = fast_exp2(fmaf(__uint_as_float(raw[i]), p.scale_log2, neg_m));
-        const float b = fast_exp2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2, neg_m));
+        const float a = fast_exp2(fmaf(__uint_as_float(raw[i]), mul, neg_m));
+        const float b = fast_exp2(fmaf(__uint_as_float(raw[i + 1]), mul, neg_m));
         part_sum[(i >> 1) & 3] += a + b;
         __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
@@ -417,11 +434,14 @@ extern "C" int asb_attention_tcgen05_supported(int hd, int group, int block_size
 
 // Attention for every request that brings more than 8 tokens in this step (others are left
 // untouched for the decode kernel). q, out: [T, H, 128] bfloat16; caches [num_blocks, KV, bs, 128].
-extern "C" int asb_prefill_attention_tcgen05_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
-                                                  const int* block_tables, const int* req_q_start,
-                                                  const int* req_pos_start, const float* sink, int num_tokens, int R,
-                                                  int H, int KV, int hd, int bs, int num_blocks, int table_width,
-                                                  int window, float scale, int* status, cudaStream_t stream) {
+// chunk, softcap (0: none): see AttnParams.
+extern "C" int asb_prefill_attention_tcgen05_masked(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                                    const int* block_tables, const int* req_q_start,
+                                                    const int* req_pos_start, const float* sink, int num_tokens, int R,
+                                                    int H, int KV, int hd, int bs, int num_blocks, int table_width,
+                                                    int window, int chunk, float scale, float softcap, int* status,
+                                                    cudaStream_t stream) {
+  if (chunk < 0 || softcap < 0.f) return asb::fail("prefill_attention_tcgen05: chunk %d and softcap %f must not be negative", chunk, (double)softcap);
   if (num_tokens == 0 || R == 0) return 0;
   if (KV < 1 || H % KV) return asb::fail("prefill_attention_tcgen05: %d heads over %d kv heads", H, KV);
   if (!asb_attention_tcgen05_supported(hd, H / KV, bs))
@@ -436,7 +456,10 @@ extern "C" int asb_prefill_attention_tcgen05_sink(void* out, const void* q, cons
   p.G = H / KV;
   p.QT = kRows / p.G;
   p.window = window;
+  p.chunk = chunk;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_log2 = softcap * 1.4426950408889634f;
+  p.scale_over_cap = softcap > 0.f ? 2.f * p.scale_log2 / softcap : 0.f;
 
   alignas(64) CUtensorMap mq, mk, mv;
   {
@@ -459,6 +482,16 @@ extern "C" int asb_prefill_attention_tcgen05_sink(void* out, const void* q, cons
   if (blocks > 0x7fffffffLL) return asb::fail("prefill_attention_tcgen05: %lld blocks exceed the grid", blocks);
   asb::launch(kern, dim3((unsigned)blocks), kThreads, kSmem, stream, mq, mk, mv, p);
   return asb::check_launch("prefill_attention_tcgen05");
+}
+
+extern "C" int asb_prefill_attention_tcgen05_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                                  const int* block_tables, const int* req_q_start,
+                                                  const int* req_pos_start, const float* sink, int num_tokens, int R,
+                                                  int H, int KV, int hd, int bs, int num_blocks, int table_width,
+                                                  int window, float scale, int* status, cudaStream_t stream) {
+  return asb_prefill_attention_tcgen05_masked(out, q, k_cache, v_cache, block_tables, req_q_start, req_pos_start, sink,
+                                              num_tokens, R, H, KV, hd, bs, num_blocks, table_width, window, 0, scale,
+                                              0.f, status, stream);
 }
 
 extern "C" int asb_prefill_attention_tcgen05(void* out, const void* q, const void* k_cache, const void* v_cache,

@@ -149,12 +149,10 @@ def paged_attention(
         require_cuda(sink)
         if sink.dtype != torch.float32 or sink.shape != (H,) or not sink.is_contiguous():
             raise KernelLibraryError(f"paged_attention: sink must be contiguous float32 [{H}]")
-    # (chunks and capped scores: the general kernel)
-    masked = chunk > 0 or softcap > 0.0
-    if q.dtype == torch.bfloat16 and not generic and not masked and lib().asb_attention_mma_supported(hd, H // KV):
-        return _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start,
-                                    num_requests, max_context, win, scale, partitions, host_q_lens, sink)  # fmt: skip
     span = min(win, chunk) if win and chunk else (win or chunk)  # a chunk bounds the keys of a row as a window does
+    if q.dtype == torch.bfloat16 and not generic and lib().asb_attention_mma_supported(hd, H // KV):
+        return _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start,
+                                    num_requests, max_context, win, scale, partitions, host_q_lens, sink, chunk, softcap, span)  # fmt: skip
     ps, np_ = partitions or plan_partitions(T, num_requests, KV, H // KV, max_context, span)
     part_m = part_l = part_acc = None
     if np_ > 1:
@@ -169,7 +167,8 @@ def paged_attention(
 
 
 def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, req_pos_start, num_requests,
-                         max_context, win, scale, partitions, host_q_lens, sink=None):  # fmt: skip
+                         max_context, win, scale, partitions, host_q_lens, sink=None, chunk=0, softcap=0.0, span=None):  # fmt: skip
+    span = win if span is None else span  # what bounds the keys of a row, for the planner
     T, H, hd = q.shape
     KV, bs = k_cache.shape[1], k_cache.shape[2]
     if host_q_lens is None:
@@ -185,9 +184,9 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
         from atomserve_b200.ops.linear import gemm_status
 
         def portions():
-            check(lib().asb_prefill_attention_tcgen05_sink(
+            check(lib().asb_prefill_attention_tcgen05_masked(
                 ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start), ptr(req_pos_start), ptr(sink),
-                T, num_requests, H, KV, hd, bs, k_cache.shape[0], block_tables.shape[1], win, float(scale),
+                T, num_requests, H, KV, hd, bs, k_cache.shape[0], block_tables.shape[1], win, chunk, float(scale), softcap,
                 ptr(gemm_status(q.device)), stream()))  # fmt: skip
 
         if not has_short:
@@ -198,7 +197,7 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
         # as in a step of its own). When the caller says how many tokens each request brings, the
         # kernel starts blocks for the short rows only and the partial results hold only those
         # rows; otherwise blocks start for every row of the step and the portions' leave at once.
-        ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win, hd)
+        ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, span, hd)
         compact = short_rows if host_q_lens is not None else 0
         scratch_rows = compact or T
         if partitions is None and scratch_rows * H * np_ * (hd + 2) * 4 > MIXED_SCRATCH_BYTES:
@@ -212,10 +211,10 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
             part_acc = torch.empty(scratch_rows * H * np_ * hd, device=q.device, dtype=torch.float32)
 
         def single_tokens():
-            check(lib().asb_paged_attention_mma_sink(
+            check(lib().asb_paged_attention_mma_masked(
                 ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
                 ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(sink), T, num_requests, H, KV, hd, bs,
-                block_tables.shape[1], win, ps, np_, float(scale), 1, 0, 0, compact, stream()))  # fmt: skip
+                block_tables.shape[1], win, chunk, ps, np_, float(scale), softcap, 1, 0, 0, compact, stream()))  # fmt: skip
             if np_ > 1 and compact:
                 check(lib().asb_attention_reduce_short(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(req_q_start),
                                                        num_requests, SHORT_ROWS, compact, H, np_, hd, dtype_code(q), stream()))  # fmt: skip
@@ -243,16 +242,16 @@ def _paged_attention_mma(q, out, k_cache, v_cache, block_tables, req_q_start, re
         return out
     ps, np_ = 1 << 30, 1
     if has_short and not has_long:
-        ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, win, hd)
+        ps, np_ = partitions or plan_decode_partitions(short_rows, KV, H // KV, max_context, span, hd)
     part_m = part_l = part_acc = None
     if np_ > 1:
         part_m = torch.empty(T * H * np_, device=q.device, dtype=torch.float32)
         part_l = torch.empty_like(part_m)
         part_acc = torch.empty(T * H * np_ * hd, device=q.device, dtype=torch.float32)
-    check(lib().asb_paged_attention_mma_sink(
+    check(lib().asb_paged_attention_mma_masked(
         ptr(out), ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(req_q_start),
         ptr(req_pos_start), ptr(part_m), ptr(part_l), ptr(part_acc), ptr(sink), T, num_requests, H, KV, hd, bs,
-        block_tables.shape[1], win, ps, np_, float(scale), int(has_short), int(has_long), int(all_single), 0,
+        block_tables.shape[1], win, chunk, ps, np_, float(scale), softcap, int(has_short), int(has_long), int(all_single), 0,
         stream()))  # fmt: skip
     if np_ > 1:
         check(lib().asb_attention_reduce(ptr(out), ptr(part_m), ptr(part_l), ptr(part_acc), T * H, np_, hd,

@@ -102,6 +102,8 @@ _SIGNATURES = {
     "asb_moe_combine_identity": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P],
     # attention within chunks of the sequence and with capped scores
     "asb_paged_attention_masked": [_P] * 11 + [_I] * 11 + [_F, _F, _I, _P],
+    "asb_paged_attention_mma_masked": [_P] * 11 + [_I] * 11 + [_F, _F, _I, _I, _I, _I, _P],
+    "asb_prefill_attention_tcgen05_masked": [_P] * 8 + [_I] * 10 + [_F, _F, _P, _P],
     # layers whose two sublayers read one stream; a hashed table of token pairs; a product over two streams
     "asb_residual_dual_norm": [_P] * 9 + [_I, _I, _F, _F, _I, _P],
     "asb_pair_embedding": [_P] * 8 + [_I] * 8 + [_P, _P],
