@@ -35,29 +35,40 @@ struct PrepareParams {
   int temp_every;  // 0: no query factor
 };
 
-// entry e of a map (of q or k) after the rotation
+// entry e of a map (of q or k) after the rotation; `cs` holds the token's cosines, then its sines
 template <typename T>
-__device__ __forceinline__ float turned(const T* map, int e, int rotary_dim, float position, const float* inv_freq) {
+__device__ __forceinline__ float turned(const T* map, int e, int rotary_dim, const float* cs) {
   const float v = asb::to_float(map[e]);
   if (e >= rotary_dim) return v;
   const int half = rotary_dim >> 1;
   const int i = e < half ? e : e - half;
-  float s, c;
-  sincosf(position * inv_freq[i], &s, &c);
+  const float c = cs[i], s = cs[half + i];
   const float w = asb::to_float(map[e < half ? e + half : e - half]);
   return e < half ? v * c - w * s : v * c + w * s;
 }
 
+// the token's cosines and sines (float32 `sincosf` of position x frequency), once per block
+__device__ __forceinline__ void fill_angles(float* cs, const PrepareParams& p, float position) {
+  const int half = p.rotary_dim >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(position * p.inv_freq[i], &cs[half + i], &cs[i]);
+  __syncthreads();
+}
+
+__device__ __forceinline__ float query_factor(const PrepareParams& p, int pos) {
+  return p.temp_every > 0 ? 1.f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.f) : 1.f;
+}
+
+// The general form: one element a thread at a time, any sizes, both element types.
 template <typename T>
 __global__ void qk_prepare_store_kernel(const PrepareParams p) {
+  extern __shared__ float cs[];
   asb::pdl_wait();
   asb::pdl_launch_dependents();
   const int t = blockIdx.x;
   const T* src = (const T*)p.proj + (size_t)t * p.row;
   const int pos = p.positions[t];
-  const float position = (float)pos;
-  float factor = 1.f;
-  if (p.temp_every > 0) factor = 1.f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.f);
+  fill_angles(cs, p, (float)pos);
+  const float factor = query_factor(p, pos);
   const int live = p.maps * p.dim;
   // queries
   T* q = (T*)p.q_out + (size_t)t * p.H * p.maps * p.hd;
@@ -66,7 +77,7 @@ __global__ void qk_prepare_store_kernel(const PrepareParams p) {
     const int j = head % p.maps;
     float v = 0.f;
     if (e >= j * p.dim && e < (j + 1) * p.dim)
-      v = turned(src + (size_t)head * p.dim, e - j * p.dim, p.rotary_dim, position, p.inv_freq) * factor;
+      v = turned(src + (size_t)head * p.dim, e - j * p.dim, p.rotary_dim, cs) * factor;
     q[i] = asb::from_float<T>(v);
   }
   const int slot = p.slots ? p.slots[t] : -1;
@@ -80,10 +91,99 @@ __global__ void qk_prepare_store_kernel(const PrepareParams p) {
     float kv = 0.f;
     if (e < live) {
       const int j = e / p.dim;
-      kv = turned(k + (size_t)g * live + j * p.dim, e - j * p.dim, p.rotary_dim, position, p.inv_freq);
+      kv = turned(k + (size_t)g * live + j * p.dim, e - j * p.dim, p.rotary_dim, cs);
     }
     ((T*)p.k_cache)[at] = asb::from_float<T>(kv);
     ((T*)p.v_cache)[at] = e < p.vdim ? v[(size_t)g * p.vdim + e] : asb::from_float<T>(0.f);
+  }
+}
+
+// The vector form (bfloat16): eight entries a thread by 16-byte loads and stores, where map, value and
+// head sizes and half the rotated entries are multiples of 8 (so no vector straddles a map's end or
+// the two halves of a rotation) and rows and pages start on 16-byte boundaries.
+struct Vec8 {
+  float v[8];
+};
+
+__device__ __forceinline__ Vec8 load8(const __nv_bfloat16* at) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(at);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  Vec8 out;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    out.v[2 * i] = f.x;
+    out.v[2 * i + 1] = f.y;
+  }
+  return out;
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16* at, const Vec8& x) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(x.v[2 * i], x.v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(at) = raw;
+}
+
+// entries e .. e + 7 of a map after the rotation
+__device__ __forceinline__ Vec8 turned8(const __nv_bfloat16* map, int e, int rotary_dim, const float* cs) {
+  Vec8 v = load8(map + e);
+  if (e >= rotary_dim) return v;
+  const int half = rotary_dim >> 1;
+  const bool low = e < half;
+  const int i = low ? e : e - half;
+  const Vec8 w = load8(map + (low ? e + half : e - half));
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const float c = cs[i + u], s = cs[half + i + u];
+    v.v[u] = low ? v.v[u] * c - w.v[u] * s : v.v[u] * c + w.v[u] * s;
+  }
+  return v;
+}
+
+__global__ void qk_prepare_store_vec_kernel(const PrepareParams p) {
+  extern __shared__ float cs[];
+  asb::pdl_wait();
+  asb::pdl_launch_dependents();
+  using T = __nv_bfloat16;
+  const int t = blockIdx.x;
+  const T* src = (const T*)p.proj + (size_t)t * p.row;
+  const int pos = p.positions[t];
+  fill_angles(cs, p, (float)pos);
+  const float factor = query_factor(p, pos);
+  const int live = p.maps * p.dim, per = p.hd >> 3;  // vectors a head
+  Vec8 zero;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) zero.v[u] = 0.f;
+  T* q = (T*)p.q_out + (size_t)t * p.H * p.maps * p.hd;
+  for (int i = threadIdx.x; i < p.H * p.maps * per; i += blockDim.x) {
+    const int head = i / per, e = (i - head * per) << 3;
+    const int j = head % p.maps;
+    Vec8 v = zero;
+    if (e >= j * p.dim && e < (j + 1) * p.dim) {
+      v = turned8(src + (size_t)head * p.dim, e - j * p.dim, p.rotary_dim, cs);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v.v[u] *= factor;
+    }
+    store8(q + (size_t)head * p.hd + e, v);
+  }
+  const int slot = p.slots ? p.slots[t] : -1;
+  if (slot < 0 || !p.k_cache) return;
+  const int page = slot / p.bs, off = slot - page * p.bs;
+  const T* k = src + (size_t)p.H * live;
+  const T* v = k + (size_t)p.KV * live;
+  for (int i = threadIdx.x; i < p.KV * per; i += blockDim.x) {
+    const int g = i / per, e = (i - g * per) << 3;
+    const size_t at = (((size_t)page * p.KV + g) * p.bs + off) * p.hd + e;
+    Vec8 kv = zero;
+    if (e < live) {
+      const int j = e / p.dim;
+      kv = turned8(k + (size_t)g * live + j * p.dim, e - j * p.dim, p.rotary_dim, cs);
+    }
+    store8((T*)p.k_cache + at, kv);
+    if (e < p.vdim) *reinterpret_cast<uint4*>((T*)p.v_cache + at) = *reinterpret_cast<const uint4*>(v + (size_t)g * p.vdim + e);
+    else store8((T*)p.v_cache + at, zero);
   }
 }
 
@@ -126,7 +226,14 @@ extern "C" int asb_qk_prepare_store(const void* proj, void* q_out, void* k_cache
   p.H = H; p.KV = KV; p.maps = maps; p.dim = dim; p.vdim = vdim; p.hd = hd; p.rotary_dim = rotary_dim; p.bs = bs;
   p.row = row;
   p.temp_coef = temp_coef; p.temp_every = temp_every;
-  ASB_DISPATCH_DTYPE(dtype, T, asb::launch(qk_prepare_store_kernel<T>, T_, 256, 0, stream, p));
+  const size_t smem = sizeof(float) * (size_t)(rotary_dim > 0 ? rotary_dim : 1);
+  const bool aligned = (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+  if (dtype == asb::kBFloat16 && aligned && dim % 8 == 0 && vdim % 8 == 0 && hd % 8 == 0 && row % 8 == 0 && rotary_dim % 16 == 0) {
+    const int vectors = (H * maps + KV) * (hd / 8);
+    asb::launch(qk_prepare_store_vec_kernel, T_, vectors >= 256 ? 256 : (vectors >= 128 ? 128 : 64), smem, stream, p);
+    return asb::check_launch("qk_prepare_store");
+  }
+  ASB_DISPATCH_DTYPE(dtype, T, asb::launch(qk_prepare_store_kernel<T>, T_, 256, smem, stream, p));
   return asb::check_launch("qk_prepare_store");
 }
 

@@ -78,7 +78,8 @@ class PairHashEmbedding(TokenEmbedding):
         super().__init__(hidden_size, prefix, vocab_size, tensor)
         if buckets < 1:
             raise ValueError(f"a pair table needs at least one bucket, got {buckets}")
-        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        # (a x) mod b = ((a mod b) x) mod b: the multipliers go to the kernel reduced, whatever their size
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev) % int(buckets), int(mul_cur) % int(buckets)
         self.pair_name = pair_tensor or prefix + "pairs"
         self.pairs: torch.Tensor | None = None
 

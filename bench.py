@@ -934,6 +934,136 @@ def time_tigesun(widths: list[int], layers: int, steps: int, warmup: int, pk: di
         print(json.dumps(line), flush=True)
 
 
+# ---- the Nipurax design beside Gefilix at equal width (`--only nipurax`) --------------------------
+
+def nipurax_shape(width: int, layers: int) -> dict:
+    """Layer sizes that resemble a served model's: differential attention with two maps of 64 a head over
+    values of 128 (so pages and kernels run at heads of 128), four query heads a kv head, in chunks of
+    1,024, half of every map turned; attention with heads of 128, capped scores, a sink and a query
+    factor; behind both 32 experts of half the width with 4 of 32 + 2 chosen and a shared expert of the
+    width, as Gefilix's. Two such layers run `layers / 2` times as the design's loop."""
+    heads = width // 128
+    moe = dict(kind="moe", expert=dict(ff=width // 2, limit=7.0), router=dict(experts=32, identity=2, top=4, scale=2.5),
+               shared=dict(ff=width, limit=7.0))  # fmt: skip
+    rot = dict(base=500000.0, dims=32, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))
+    pair = [
+        dict(type="attention", mixer=dict(heads=heads, kv_heads=max(heads // 4, 1), dim=64, vdim=128, scale=64 ** -0.5, diff=0.5,
+                                          mask=dict(size=1024), rot=rot), mlp=moe),
+        dict(type="attention_2", mixer=dict(heads=heads, kv_heads=max(heads // 4, 1), dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0,
+                                            q_temp=dict(coef=0.5, every=128)), mlp=moe),
+    ]  # fmt: skip
+    return dict(architecture="Nipurax", vocab=32000, width=width, layers=pair, norm=dict(eps=1e-6), residual_mult=0.5,
+                embedding=dict(bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)), loop=dict(start=0, stop=2, times=max(layers // 2, 1)))  # fmt: skip
+
+
+def time_nipurax(widths: list[int], layers: int, steps: int, warmup: int, pk: dict) -> None:
+    """Prefill and decode of a Nipurax model and of a Gefilix model of the same width and depth (random
+    weights), through the step function, and the design's own kernels one by one against their
+    rooflines beside the like kernels of the other models."""
+    import torch
+
+    from atomserve_b200 import ops
+    from atomserve_b200.ops.status import status_for
+
+    timed, model_times = design_timers(steps, warmup)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
+    bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    bf = torch.bfloat16
+    for width in widths:
+        line = {"only": "nipurax", "width": width, "layers": layers, "peaks": pk["source"],
+                "nipurax": model_times(nipurax_shape(width, layers), 32000), "gefilix": model_times(gefilix_shape(width, layers), 32000)}
+        kern = {}
+        T, B, ctx, bs = PROMPT_TOKENS, 64, PROMPT_TOKENS, BLOCK_SIZE
+        H, KV, hd = width // 128, max(width // 512, 1), 128
+        pages_per = ctx // bs
+        tables = i32([[r * pages_per + j for j in range(pages_per)] for r in range(B)])
+        starts, at = i32(list(range(B + 1))), i32([ctx - 1] * B)
+        t1, whole, first = i32([list(range(pages_per))]), i32([0, T]), i32([0])  # (made once: a tensor from a list is a copy and a wait)
+        k_pages = torch.randn(B * pages_per, KV, bs, hd, device="cuda", dtype=bf)
+        v_pages = torch.randn_like(k_pages)
+        sink = torch.zeros(H, device="cuda")
+        # attention: the two maps of a head as two query heads (2 H of them) within chunks of 1,024; capped scores
+        # with a sink; and the plain causal attention of the other models, all at heads of 128. Decode: B single
+        # tokens at context ctx (a chunked layer reads the keys of the last chunk only); prefill: one prompt of T.
+        for name, heads, more, keys in (("differential_attention", 2 * H, dict(chunk=1024), 1024),
+                                        ("capped_sink_attention", H, dict(softcap=30.0, sink=sink), ctx),
+                                        ("paged_attention", H, {}, ctx)):  # fmt: skip
+            q = torch.randn(B, heads, hd, device="cuda", dtype=bf)
+            ms = timed(lambda: ops.paged_attention(q, k_pages, v_pages, tables, starts, at, num_requests=B, max_context=ctx, window=None,
+                                                   scale=0.088, host_q_lens=[1] * B, **more))  # fmt: skip
+            kern[f"{name}_decode_b64"] = {"ms": round(ms, 4), "hbm_frac": round(2.0 * B * keys * KV * hd * 2 / (ms * 1e-3) / bw, 3)}
+            qp = torch.randn(T, heads, hd, device="cuda", dtype=bf)
+            seen = sum(min(t % keys + 1, keys) if keys < ctx else t + 1 for t in range(T))
+            ms = timed(lambda: ops.paged_attention(qp, k_pages, v_pages, t1, whole, first, num_requests=1, max_context=T, window=None,
+                                                   scale=0.088, host_q_lens=[T], **more), 4)  # fmt: skip
+            # (a map's scores need 64 entries a key, its values 128; the kernels multiply the padded 128 for both)
+            flops = 2.0 * seen * heads * (64 + 128) if name == "differential_attention" else 4.0 * seen * heads * hd
+            kern[f"{name}_prefill"] = {"ms": round(ms, 3), "tc_frac": round(flops / (ms * 1e-3) / tf, 4)}
+        # rotation of every map, query factor and page write, beside Qwen3's q/k norm + rotation + page write
+        positions, slots = i32(list(range(T))), i32(list(range(T)))
+        inv_freq = (1.0 / 500000.0 ** (torch.arange(0, 32, 2, dtype=torch.float32) / 32)).cuda()
+        proj2 = torch.randn(T, (H + KV) * 2 * 64 + KV * 128, device="cuda", dtype=bf)
+        ms = timed(lambda: ops.qk_prepare_store(proj2, H, KV, 2, 64, 128, hd, positions, inv_freq=inv_freq, rotary_dim=32, slots=slots,
+                                                k_cache=k_pages, v_cache=v_pages))  # fmt: skip
+        kern["qk_prepare_store_two_maps"] = {"ms": round(ms, 4), "hbm_frac": round(T * ((H + KV) * 128 + KV * 128 + 2 * H * hd + 2 * KV * hd) * 2 / (ms * 1e-3) / bw, 3)}
+        proj1 = torch.randn(T, (H + 2 * KV) * hd, device="cuda", dtype=bf)
+        ms = timed(lambda: ops.qk_prepare_store(proj1, H, KV, 1, hd, hd, hd, positions, temperature=(0.5, 128), slots=slots,
+                                                k_cache=k_pages, v_cache=v_pages))  # fmt: skip
+        kern["qk_prepare_store_query_factor"] = {"ms": round(ms, 4), "hbm_frac": round(T * (2 * H + 4 * KV) * hd * 2 / (ms * 1e-3) / bw, 3)}
+        g1 = torch.ones(hd, device="cuda")
+        inv128 = (1.0 / 1000000.0 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd)).cuda()
+        ms = timed(lambda: ops.qk_norm_rope_store(proj1, H, KV, hd, positions, q_gain=g1, k_gain=g1, eps=1e-6, inv_freq=inv128,
+                                                  rotary_dim=hd, slots=slots, k_cache=k_pages, v_cache=v_pages))  # fmt: skip
+        kern["qk_norm_rope_store"] = {"ms": round(ms, 4), "hbm_frac": round(T * (2 * H + 4 * KV) * hd * 2 / (ms * 1e-3) / bw, 3)}
+        maps = torch.randn(T, 2 * H, hd, device="cuda", dtype=bf)
+        ms = timed(lambda: ops.differential_combine(maps, 128, 0.6, 0.5, 1e-6))
+        kern["differential_combine"] = {"ms": round(ms, 4), "hbm_frac": round(T * 3 * H * hd * 2 / (ms * 1e-3) / bw, 3)}
+        gate = torch.randn(T, H * hd, device="cuda", dtype=bf)
+        o32 = torch.randn(T, H * hd, device="cuda")
+        gain_o = torch.ones(H * hd, device="cuda")
+        ms = timed(lambda: ops.head_norm_gate(o32, gate, H, gain=gain_o, eps=1e-6))
+        kern["head_norm_gate"] = {"ms": round(ms, 4), "hbm_frac": round(T * H * hd * 8 / (ms * 1e-3) / bw, 3)}
+        # the sum of a layer and both norms of the next, beside Gefilix's norm after the sum (T rows and B rows)
+        x, y1, y2 = (torch.randn(T, width, device="cuda") for _ in range(3))
+        gain = torch.ones(width, device="cuda")
+        for name, rows in (("prefill", T), ("decode_b64", B)):
+            ms = timed(lambda: ops.residual_dual_norm(x[:rows], y1[:rows], y2[:rows], 0.5, gain, gain, 1e-6, bf))
+            kern[f"residual_dual_norm_{name}"] = {"ms": round(ms, 4), "hbm_frac": round(rows * width * 20 / (ms * 1e-3) / bw, 3)}
+            ms = timed(lambda: ops.scaled_add_rms_norm(x[:rows], y1[:rows], 1.0, gain, 1e-6, bf))
+            kern[f"scaled_add_rms_norm_{name}"] = {"ms": round(ms, 4), "hbm_frac": round(rows * width * 14 / (ms * 1e-3) / bw, 3)}
+        # the embedding with its table of pairs beside the scaled embedding, and the two streams side by side
+        table, pairs = torch.randn(32000, width, device="cuda", dtype=bf), torch.randn(65522, width, device="cuda", dtype=bf)
+        ids, last = i32([(7 + 13 * i) % 32000 for i in range(T)]), torch.zeros(B + 1, 1, dtype=torch.int32, device="cuda")
+        status = status_for(torch.device("cuda")).embedding
+        ms = timed(lambda: ops.pair_embedding(ids, positions, whole, first, last, table, pairs, 1000003, 31, status))
+        kern["pair_embedding"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 8 / (ms * 1e-3) / bw, 3)}
+        ms = timed(lambda: ops.embedding_scaled(ids, table, 1.0, status))
+        kern["embedding_scaled"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 6 / (ms * 1e-3) / bw, 3)}
+        ms = timed(lambda: ops.concat_cast(x, y1, bf))
+        kern["concat_cast"] = {"ms": round(ms, 4), "hbm_frac": round(T * width * 12 / (ms * 1e-3) / bw, 3)}
+        # the experts: selection with offsets over 32 + 2 router outputs, and the weighted sum with identity experts,
+        # beside the same kernels as Gefilix calls them (grouped selection, no identity experts); the grouped products
+        # between them are the same launches for both designs
+        for name, rows in (("prefill", T), ("decode_b64", B)):
+            z = torch.randn(rows, 34, device="cuda")
+            offsets = torch.zeros(34, device="cuda")
+            ms = timed(lambda: ops.route(z, experts=34, top=4, scale=2.5, softmax=True, renormalise=False, bias=offsets))
+            kern[f"route_offsets_{name}"] = {"ms": round(ms, 4)}
+            ms = timed(lambda: ops.route(z, experts=32, top=4, groups=4, group_top=2, keep=2, scale=2.5))
+            kern[f"route_groups_{name}"] = {"ms": round(ms, 4)}
+            ids4, weights, _ = ops.route(z, experts=34, top=4, scale=2.5, softmax=True, renormalise=False, bias=offsets)
+            _, _, pair_row = ops.group_by_expert(ids4, 34)
+            y = torch.randn(rows * 4, width, device="cuda")
+            shared = torch.randn(rows, width, device="cuda")
+            hrows = torch.randn(rows, width, device="cuda", dtype=bf)
+            ms = timed(lambda: ops.combine(y, pair_row, weights, shared, None, identity=(ids4, hrows, 32)))
+            kern[f"combine_identity_{name}"] = {"ms": round(ms, 4), "hbm_frac": round(rows * width * (4 * 4 + 4 + 4 + 2) / (ms * 1e-3) / bw, 3)}
+            ms = timed(lambda: ops.combine(y, pair_row, weights, shared, None))
+            kern[f"combine_{name}"] = {"ms": round(ms, 4), "hbm_frac": round(rows * width * (4 * 4 + 4 + 4) / (ms * 1e-3) / bw, 3)}
+        line["kernels"] = kern
+        print(json.dumps(line), flush=True)
+
+
 def tigesun_inner(width: int, ff: int, w_gu, b_gu):
     """A gated feed-forward part holding the given stacked gate and up rows ([2 ff, width], gate first)."""
     import torch
@@ -1001,7 +1131,7 @@ def main() -> int:
                         help="fewer layers than the model has (same layer sizes), where time or memory needs it")  # fmt: skip
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling", "designs", "zogepel", "tigesun"], help="time just this (for profiling small cases and the other shapes)")
+    parser.add_argument("--only", choices=["decode", "prefill", "gemm", "serve", "attention", "sampling", "designs", "zogepel", "tigesun", "nipurax"], help="time just this (for profiling small cases and the other shapes)")
     parser.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="with --only decode/prefill/serve: layer sizes of Qwen3-8B, -14B or -32B")
     parser.add_argument("--context", type=int, default=PROMPT_TOKENS, help="with --only decode: tokens each request holds when decoding starts")
     parser.add_argument("--requests", type=int, default=32, help="with --only serve: requests submitted at once")
@@ -1009,7 +1139,7 @@ def main() -> int:
     parser.add_argument("--budget", type=int, default=512, help="with --only serve: the scheduler's token budget per step")
     parser.add_argument("--gemm-shape", default="all", help="with --only gemm: qkv, o, gate_up, down, lm_head or all")
     parser.add_argument("--gemm-tokens", default="1,8,64,2048", help="with --only gemm: token counts, comma-separated")
-    parser.add_argument("--widths", default="2048,4096", help="with --only designs, zogepel or tigesun: model widths, comma-separated")
+    parser.add_argument("--widths", default="2048,4096", help="with --only designs, zogepel, tigesun or nipurax: model widths, comma-separated")
     parser.add_argument("--timeline", action="store_true", help="with --only gemm: where a decode-size call's time goes")
     args = parser.parse_args()
     args.layers_given = any(a == "--layers" or a.startswith("--layers=") for a in sys.argv[1:])
@@ -1040,6 +1170,9 @@ def main() -> int:
         return 0
     if args.only == "tigesun":
         time_tigesun([int(w) for w in args.widths.split(",")], args.layers if args.layers_given else 4, max(args.steps // 4, 8), warmup, pk)
+        return 0
+    if args.only == "nipurax":
+        time_nipurax([int(w) for w in args.widths.split(",")], args.layers if args.layers_given else 4, max(args.steps // 4, 8), warmup, pk)
         return 0
     if args.only == "gemm" and args.timeline:
         gemm_timelines(args.gemm_shape, [int(t) for t in args.gemm_tokens.split(",")])
