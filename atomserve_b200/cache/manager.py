@@ -9,9 +9,10 @@ width]`, and its own allocator and, per request, its own block table. Position p
 `page * block_size + offset` (atomserve/kv_cache.py:9-14). Pools start zeroed so that no read
 can meet a NaN (atomserve/kv_cache.py:112-118).
 
-Pages come back when a request ends or is preempted, and, in a windowed group, as soon as the
-window has passed them: before a step that starts at position c, pages wholly below
-c - window + 1 are released and their table entries set to -1.
+Pages come back when a request ends or is preempted, and, in a group with a window or with
+chunks, as soon as no later position can read them: before a step that starts at position c,
+pages wholly below c - window + 1 (below the start of c's chunk) are released and their table
+entries set to -1.
 
 The reference has one uniform pool (atomserve/kv_cache.py:89-135) and lets the scheduler talk to
 the allocator directly (atomserve/scheduler.py:204-254); here the scheduler talks to this
@@ -65,6 +66,11 @@ class CacheGroup:
     def window(self) -> int | None:
         return self.spec.window
 
+    @property
+    def releases_early(self) -> bool:
+        """Whether pages of this group are given back before a request ends (a window, chunks)."""
+        return self.spec.window is not None or self.spec.chunk is not None
+
 
 class CacheManager:
     def __init__(
@@ -97,7 +103,7 @@ class CacheManager:
                 self.entry_state[i] = {
                     s.name: self.state.register(f"{i}.{s.name}", tuple(s.shape), s.dtype) for s in states
                 }
-        self._windowed = any(g.window is not None for g in self.groups)  # only windows release pages early
+        self._windowed = any(g.releases_early for g in self.groups)  # only windows and chunks release pages early
         if self.device is not None:
             for g in self.groups:
                 for t in g.spec.tensors:
@@ -117,7 +123,7 @@ class CacheManager:
     def supports_prefix_caching(self) -> bool:
         """Sharing pages by content is sound only when all that a request keeps are pages of one
         unwindowed group (a window releases pages, state is not content-addressed)."""
-        return len(self.groups) == 1 and self.groups[0].window is None and not self.entry_state
+        return len(self.groups) == 1 and not self.groups[0].releases_early and not self.entry_state
 
     @property
     def num_free_blocks(self) -> int:
@@ -139,14 +145,13 @@ class CacheManager:
 
     def first_needed_block(self, group: CacheGroup, start: int) -> int:
         """The lowest logical page a step starting at position `start` can still read."""
-        if group.window is None:
-            return 0
-        return max(0, start - group.window + 1) // self.block_size
+        return group.spec.first_needed(start) // self.block_size
 
     def release_passed(self, rc: RequestCache, start: int) -> None:
-        """Give back the pages that every window has passed before position `start` runs."""
+        """Give back the pages that no position from `start` on can read (a window has passed them, or
+        they lie before the chunk that `start` is in)."""
         for g, table in zip(self.groups, rc.block_tables):
-            if g.window is None:
+            if not g.releases_early:
                 continue
             upto = min(self.first_needed_block(g, start), len(table))
             passed = [b for b in table[:upto] if b >= 0]

@@ -173,7 +173,7 @@ class ModelRunner:
             for g, table in zip(groups, r.cache.block_tables):
                 if (r.start + n) > len(table) * bs:
                     raise ValueError(f"block table holds {len(table) * bs} slots, the row needs {r.start + n}")
-                if g.window is not None:  # only windows release pages before a request ends
+                if g.releases_early:  # only windows and chunks release pages before a request ends
                     first = self.cache.first_needed_block(g, r.start)
                     if any(b < 0 for b in table[first : -(-(r.start + n) // bs)]):
                         raise ValueError("a page the row still reads has been released")

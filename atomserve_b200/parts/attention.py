@@ -62,7 +62,7 @@ class GQAttention(Mixer):
         self.qkv_proj = self.o_proj = self.q_gain = self.k_gain = self.sink = None
 
     def cache_spec(self) -> PageSpec:
-        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window, self.chunk)
 
     def tensor_specs(self) -> list[TensorSpec]:
         n, d, kd, vd = self.names, self.hidden_size, self.key_dim, self.value_dim

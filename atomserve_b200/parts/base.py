@@ -39,22 +39,34 @@ class PageTensor:
 
 @dataclass(frozen=True)
 class PageSpec:
-    """What a mixer keeps in pages: the tensors each page holds, and `window`: only the last
-    `window` positions are ever read, so older pages can be given back early. Entries of the run
-    order with equal specs share a group of pools, an allocator and the requests' block tables."""
+    """What a mixer keeps in pages: the tensors each page holds, and what lets pages go early:
+    `window` (only the last `window` positions are ever read) and `chunk` (a position reads only
+    its own run of `chunk` positions, counted from the request's start), so older pages can be
+    given back before the request ends. Entries of the run order with equal specs share a group of
+    pools, an allocator and the requests' block tables."""
 
     tensors: tuple[PageTensor, ...]
     window: int | None = None
+    chunk: int | None = None
 
     @property
     def values_per_token(self) -> int:
         return sum(t.heads * t.width for t in self.tensors)
 
+    def first_needed(self, start: int) -> int:
+        """The lowest position that a step starting at position `start` can still read."""
+        lowest = 0
+        if self.window is not None:
+            lowest = max(lowest, start - self.window + 1)
+        if self.chunk is not None:
+            lowest = max(lowest, start - start % self.chunk)
+        return lowest
 
-def KVCacheSpec(num_kv_heads: int, head_dim: int, window: int | None = None) -> PageSpec:
+
+def KVCacheSpec(num_kv_heads: int, head_dim: int, window: int | None = None, chunk: int | None = None) -> PageSpec:
     """The usual pages: keys and values, `num_kv_heads * head_dim` of each per token, as tensors
     "k" and "v"."""
-    return PageSpec((PageTensor("k", num_kv_heads, head_dim), PageTensor("v", num_kv_heads, head_dim)), window)
+    return PageSpec((PageTensor("k", num_kv_heads, head_dim), PageTensor("v", num_kv_heads, head_dim)), window, chunk)
 
 
 @dataclass(frozen=True)

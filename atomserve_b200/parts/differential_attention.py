@@ -43,7 +43,7 @@ class DifferentialAttention(Mixer):
         self.lam = 0.0
 
     def cache_spec(self) -> PageSpec:
-        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window, self.chunk)
 
     def tensor_specs(self) -> list[TensorSpec]:
         p, d = self.prefix, self.hidden_size

@@ -136,6 +136,31 @@ def test_window_pages_come_back_and_full_pages_stay():
     assert cache.num_free_blocks == 32
 
 
+def test_pages_before_the_current_chunk_come_back():
+    """A group whose positions read only their own run of 20 positions: before a step that starts
+    at c, the pages wholly below c - c % 20 go; a group with both a chunk and a window lets go
+    whatever either allows; equal specs with and without a chunk are groups of their own."""
+    chunked, both = KVCacheSpec(2, 16, None, 20), KVCacheSpec(2, 16, 12, 20)
+    cache = CacheManager([(FULL, []), (chunked, []), (both, []), (chunked, [])], block_size=8, num_blocks=32, num_state_slots=2)
+    assert len(cache.groups) == 3 and not cache.supports_prefix_caching
+    rc = cache.new_request()
+    cache.admit(rc)
+    pos = 0
+    for n in [19, 1, 1, 30, 1, 1, 1, 1, 1, 1, 1, 1, 9]:
+        assert cache.reserve(rc, pos, n)
+        start = pos
+        pos += n
+        full, ch, cw = rc.block_tables
+        assert all(b >= 0 for b in full) and len(full) == blocks_for_tokens(pos, 8)
+        first = (start - start % 20) // 8
+        assert all(b == -1 for b in ch[:first]) and all(b >= 0 for b in ch[first:]), (start, ch)
+        first = max(start - start % 20, start - 12 + 1, 0) // 8
+        assert all(b == -1 for b in cw[:first]) and all(b >= 0 for b in cw[first:]), (start, cw)
+    assert chunked.first_needed(59) == 40 and chunked.first_needed(60) == 60 and both.first_needed(59) == 48 and FULL.first_needed(59) == 0
+    cache.free(rc)
+    assert cache.num_free_blocks == 32
+
+
 def test_reservation_is_all_groups_or_none():
     cache = CacheManager([(FULL, []), (KVCacheSpec(1, 8, None), [])], block_size=4, num_blocks=4, num_state_slots=2)
     a, b = cache.new_request(), cache.new_request()

@@ -38,6 +38,7 @@ def test_run_order_and_what_each_entry_keeps():
     # a head of two maps of 12 under values of 40 runs at 40; of two maps of 20 over values of 24 at 40 too
     assert needs[1][0].tensors[0].width == 40 and needs[7][0].tensors[0].width == 40 and needs[0][0].tensors[0].width == 24
     assert needs[1][0].tensors[0].heads == 2  # the two maps of a kv head share one key head
+    assert needs[1][0].chunk == 10 and needs[7][0].chunk == 33 and needs[0][0].chunk is None  # pages of passed chunks go back
     no_loop, _ = NIPURAX["b"]
     arch, config = config_from_dict(no_loop)
     spec = arch.build_spec(config)

@@ -436,6 +436,11 @@ def test_long_decoding(models, dtype):
             logits = rp.step([dict(id="x", tokens=[p[j]], want=[0])], end=[])
             if j % 9 == 0 or j > 410:
                 judged(logits, ref[j : j + 1], dtype, f"{name} decode position {j}", tol[j : j + 1], {k: v[j : j + 1] for k, v in sure.items()})
+        held = rp.live["x"][0]
+        chunked = [(g.spec.chunk, table) for g, table in zip(rp.cache.groups, held.block_tables) if g.spec.chunk]
+        assert chunked, "no chunked layer kept pages of its own"
+        for chunk, table in chunked:  # pages before the current chunk have gone back to the pool
+            assert sum(b >= 0 for b in table) <= -(-chunk // bs) + 1 and len(table) == -(-len(p) // bs)
 
 
 def test_the_stream_after_every_layer(models):
