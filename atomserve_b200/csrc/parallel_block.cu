@@ -94,6 +94,24 @@ __global__ void pair_embedding_kernel(float* __restrict__ out, const T* __restri
   const long long hashed = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
   const T* a = table + (size_t)id * width;
   const T* b = pairs + (size_t)(prev < 0 ? buckets : (int)hashed) * width;
+  if (sizeof(T) == 2 && width % 8 == 0 && (((uintptr_t)table | (uintptr_t)pairs | (uintptr_t)out) & 15) == 0) {
+    // eight entries a thread: one 16-byte load from each table, two 16-byte stores
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+      const uint4 ra = *reinterpret_cast<const uint4*>(a + i), rb = *reinterpret_cast<const uint4*>(b + i);
+      const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&ra);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&rb);
+      float sum[8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 fa = __bfloat1622float2(ha[u]), fb = __bfloat1622float2(hb[u]);
+        sum[2 * u] = fa.x + fb.x;
+        sum[2 * u + 1] = fa.y + fb.y;
+      }
+      *reinterpret_cast<float4*>(dst + i) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+      *reinterpret_cast<float4*>(dst + i + 4) = make_float4(sum[4], sum[5], sum[6], sum[7]);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = asb::to_float(a[i]) + asb::to_float(b[i]);
 }
 
@@ -102,6 +120,24 @@ __global__ void concat_cast_kernel(T* __restrict__ out, const float* __restrict_
                                    int width, long long total) {
   asb::pdl_wait();
   asb::pdl_launch_dependents();
+  if (width % 4 == 0 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0) {
+    // four entries a thread (no group of four straddles the two halves of a row)
+    for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < total; i += (long long)gridDim.x * blockDim.x * 4) {
+      const long long r = i / (2 * width);
+      const int c = (int)(i - r * 2 * width);
+      const float4 v = *reinterpret_cast<const float4*>(c < width ? a + r * width + c : b + r * width + c - width);
+      if (sizeof(T) == 2) {  // one 8-byte store
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(out + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+      } else {
+        out[i] = asb::from_float<T>(v.x);
+        out[i + 1] = asb::from_float<T>(v.y);
+        out[i + 2] = asb::from_float<T>(v.z);
+        out[i + 3] = asb::from_float<T>(v.w);
+      }
+    }
+    return;
+  }
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / (2 * width);
     const int c = (int)(i - r * 2 * width);
@@ -130,7 +166,7 @@ extern "C" int asb_pair_embedding(float* out, const void* table, const void* pai
                                   int mul_prev, int mul_cur, int dtype, int* status, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (buckets < 1 || R < 1) return asb::fail("pair_embedding: %d buckets, %d requests", buckets, R);
-  ASB_DISPATCH_DTYPE(dtype, T, asb::launch(pair_embedding_kernel<T>, num_tokens, threads_for(width), 0, stream, out,
+  ASB_DISPATCH_DTYPE(dtype, T, asb::launch(pair_embedding_kernel<T>, num_tokens, threads_for(sizeof(T) == 2 && width % 8 == 0 ? width / 8 : width), 0, stream, out,
                                            (const T*)table, (const T*)pairs, ids, positions, req_q_start, state_slots,
                                            last_id, R, width, vocab, buckets, mul_prev, mul_cur, status));
   return asb::check_launch("pair_embedding");
@@ -140,7 +176,7 @@ extern "C" int asb_concat_cast(void* out, const float* a, const float* b, int n,
                                cudaStream_t stream) {
   if (n == 0) return 0;
   const long long total = (long long)n * 2 * width;
-  const long long blocks = (total + 255) / 256;
+  const long long blocks = (total / (width % 4 == 0 ? 4 : 1) + 255) / 256;
   ASB_DISPATCH_DTYPE(dtype, T, asb::launch(concat_cast_kernel<T>, (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256,
                                            0, stream, (T*)out, a, b, width, total));
   return asb::check_launch("concat_cast");
