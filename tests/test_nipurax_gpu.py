@@ -243,6 +243,11 @@ MIXERS = [
     sink_attention(4, 4, 12, 20, 0.6),
     sink_attention(8, 2, 128, 128, 0.15, temp=(0.5, 9), softcap=20.0),
     sink_attention(4, 1, 64, 64, 0.25, softcap=2.0),
+    # more query heads (or maps) a kv head than one block of the tensor-core kernels takes
+    diff_attention(16, 1, 32, 64, 0.3, 0.5, 20, rot=(100.0, 16, None)),
+    diff_attention(10, 1, 64, 128, 0.2, 0.3, 12),
+    sink_attention(20, 1, 128, 128, 0.15, temp=(0.3, 5), softcap=10.0),
+    sink_attention(34, 2, 64, 64, 0.2, softcap=6.0),
 ]  # fmt: skip
 
 
