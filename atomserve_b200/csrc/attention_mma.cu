@@ -360,12 +360,17 @@ decode_attention_kernel(const MmaParams p) {
     if (kt0 + key0 < key_hi && kt0 + key0 + 16 > key_lo) {
       float s[2][4];
       qk_16keys<HD>(s, qf, k_stage(it), key0, lane, p.scale);
+      if (p.softcap > 0.f) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[j][e] = capped(s[j][e], p.softcap);
+      }
       // mask by absolute key position; both rows of a thread share the token, hence the mask
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          if (p.softcap > 0.f) s[j][e] = capped(s[j][e], p.softcap);
           const int key = kt0 + key0 + j * 8 + (lane & 3) * 2 + (e & 1);
           if (key < key_lo || key >= key_hi) s[j][e] = -INFINITY;
         }
@@ -609,12 +614,17 @@ prefill_attention_kernel(const MmaParams p) {
       const bool inside = warp_full && kt0 + kKeyTile <= warp_min_pos + 1 && kt0 >= key_lo && kt0 + kKeyTile <= key_hi &&
                           (p.window <= 0 || kt0 > warp_max_pos - p.window) && kt0 >= warp_chunk_lo;
       float rmax[2] = {-INFINITY, -INFINITY};
+      if (cap2 > 0.f) {
+        // (a group no row sees holds -inf, which the cap turns into -cap: such tiles are never `inside`)
+#pragma unroll
+        for (int j = 0; j < kKeyTile / 8; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[j][e] = capped(s[j][e], cap2);
+      }
 #pragma unroll
       for (int j = 0; j < kKeyTile / 8; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          // (a group no row sees holds -inf, which the cap turns into -cap: such tiles are never `inside`)
-          if (cap2 > 0.f) s[j][e] = capped(s[j][e], cap2);
           if (!inside) {
             const int key = kt0 + j * 8 + (lane & 3) * 2 + (e & 1);
             const int qp = qpos[e >> 1];
