@@ -945,12 +945,12 @@ def nipurax_shape(width: int, layers: int) -> dict:
     heads = width // 128
     moe = dict(kind="moe", expert=dict(ff=width // 2, limit=7.0), router=dict(experts=32, identity=2, top=4, scale=2.5),
                shared=dict(ff=width, limit=7.0))  # fmt: skip
-    rot = dict(base=500000.0, dims=32, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))
+    rot = dict(base=1000000.0, dims=32, scaling=dict(factor=4.0, low=1.0, high=8.0, original=4096))
     pair = [
-        dict(type="attention", mixer=dict(heads=heads, kv_heads=max(heads // 4, 1), dim=64, vdim=128, scale=64 ** -0.5, diff=0.5,
+        dict(type="attention", mixer=dict(heads=heads, kv_heads=max(heads // 4, 1), dim=64, vdim=128, scale=64 ** -0.5, diff=0.4,
                                           mask=dict(size=1024), rot=rot), mlp=moe),
-        dict(type="attention_2", mixer=dict(heads=heads, kv_heads=max(heads // 4, 1), dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0,
-                                            q_temp=dict(coef=0.5, every=128)), mlp=moe),
+        dict(type="attention_2", mixer=dict(heads=heads, kv_heads=max(heads // 4, 1), dim=128, vdim=128, scale=128 ** -0.5, softcap=50.0,
+                                            q_temp=dict(coef=0.2, every=256)), mlp=moe),
     ]  # fmt: skip
     return dict(architecture="Nipurax", vocab=32000, width=width, layers=pair, norm=dict(eps=1e-6), residual_mult=0.5,
                 embedding=dict(bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)), loop=dict(start=0, stop=2, times=max(layers // 2, 1)))  # fmt: skip
@@ -986,7 +986,7 @@ def time_nipurax(widths: list[int], layers: int, steps: int, warmup: int, pk: di
         # with a sink; and the plain causal attention of the other models, all at heads of 128. Decode: B single
         # tokens at context ctx (a chunked layer reads the keys of the last chunk only); prefill: one prompt of T.
         for name, heads, more, keys in (("differential_attention", 2 * H, dict(chunk=1024), 1024),
-                                        ("capped_sink_attention", H, dict(softcap=30.0, sink=sink), ctx),
+                                        ("capped_sink_attention", H, dict(softcap=50.0, sink=sink), ctx),
                                         ("paged_attention", H, {}, ctx)):  # fmt: skip
             q = torch.randn(B, heads, hd, device="cuda", dtype=bf)
             ms = timed(lambda: ops.paged_attention(q, k_pages, v_pages, tables, starts, at, num_requests=B, max_context=ctx, window=None,
@@ -1001,13 +1001,13 @@ def time_nipurax(widths: list[int], layers: int, steps: int, warmup: int, pk: di
             kern[f"{name}_prefill"] = {"ms": round(ms, 3), "tc_frac": round(flops / (ms * 1e-3) / tf, 4)}
         # rotation of every map, query factor and page write, beside Qwen3's q/k norm + rotation + page write
         positions, slots = i32(list(range(T))), i32(list(range(T)))
-        inv_freq = (1.0 / 500000.0 ** (torch.arange(0, 32, 2, dtype=torch.float32) / 32)).cuda()
+        inv_freq = (1.0 / 1000000.0 ** (torch.arange(0, 32, 2, dtype=torch.float32) / 32)).cuda()
         proj2 = torch.randn(T, (H + KV) * 2 * 64 + KV * 128, device="cuda", dtype=bf)
         ms = timed(lambda: ops.qk_prepare_store(proj2, H, KV, 2, 64, 128, hd, positions, inv_freq=inv_freq, rotary_dim=32, slots=slots,
                                                 k_cache=k_pages, v_cache=v_pages))  # fmt: skip
         kern["qk_prepare_store_two_maps"] = {"ms": round(ms, 4), "hbm_frac": round(T * ((H + KV) * 128 + KV * 128 + 2 * H * hd + 2 * KV * hd) * 2 / (ms * 1e-3) / bw, 3)}
         proj1 = torch.randn(T, (H + 2 * KV) * hd, device="cuda", dtype=bf)
-        ms = timed(lambda: ops.qk_prepare_store(proj1, H, KV, 1, hd, hd, hd, positions, temperature=(0.5, 128), slots=slots,
+        ms = timed(lambda: ops.qk_prepare_store(proj1, H, KV, 1, hd, hd, hd, positions, temperature=(0.2, 256), slots=slots,
                                                 k_cache=k_pages, v_cache=v_pages))  # fmt: skip
         kern["qk_prepare_store_query_factor"] = {"ms": round(ms, 4), "hbm_frac": round(T * (2 * H + 4 * KV) * hd * 2 / (ms * 1e-3) / bw, 3)}
         g1 = torch.ones(hd, device="cuda")
@@ -1016,7 +1016,7 @@ def time_nipurax(widths: list[int], layers: int, steps: int, warmup: int, pk: di
                                                   rotary_dim=hd, slots=slots, k_cache=k_pages, v_cache=v_pages))  # fmt: skip
         kern["qk_norm_rope_store"] = {"ms": round(ms, 4), "hbm_frac": round(T * (2 * H + 4 * KV) * hd * 2 / (ms * 1e-3) / bw, 3)}
         maps = torch.randn(T, 2 * H, hd, device="cuda", dtype=bf)
-        ms = timed(lambda: ops.differential_combine(maps, 128, 0.6, 0.5, 1e-6))
+        ms = timed(lambda: ops.differential_combine(maps, 128, 0.45, 0.6, 1e-6))
         kern["differential_combine"] = {"ms": round(ms, 4), "hbm_frac": round(T * 3 * H * hd * 2 / (ms * 1e-3) / bw, 3)}
         gate = torch.randn(T, H * hd, device="cuda", dtype=bf)
         o32 = torch.randn(T, H * hd, device="cuda")

@@ -90,7 +90,7 @@ def test_the_package_makes_the_same_frequencies():
     from atomserve_b200.parts.spec import PartSpec
 
     for base, dims, scaling in [(100.0, 8, (4.0, 1.0, 4.0, 64)), (50.0, 4, (16.0, 2.0, 3.0, 8)), (1000.0, 12, (2.0, 100.0, 400.0, 64)),
-                                (500000.0, 32, (2.0, 0.001, 0.01, 4096)), (10000.0, 32, (8.0, 1.0, 4.0, 128))]:  # fmt: skip
+                                (400000.0, 32, (2.0, 0.001, 0.01, 4096)), (10000.0, 32, (6.0, 1.0, 3.0, 128))]:  # fmt: skip
         rot = dict(base=base, dims=dims, scaling=dict(zip(("factor", "low", "high", "original"), scaling)))
         part = build_part("position", PartSpec("band_scaled_rotary", dict(head_dim=dims, theta=base, rotary_dim=dims, factor=scaling[0],
                                                                           low=scaling[1], high=scaling[2], original=scaling[3])), 8)  # fmt: skip

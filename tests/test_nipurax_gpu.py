@@ -103,7 +103,7 @@ def test_opening_of_a_pass(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("maps,dim,vdim,dims,temp", [(2, 12, 40, 8, None), (2, 20, 24, 20, None), (1, 24, 16, 0, (0.7, 7)), (2, 64, 128, 32, None),
-                                                     (1, 64, 64, 0, (0.5, 128)), (2, 48, 64, 24, (1.0, 3)), (1, 16, 16, 16, None)])  # fmt: skip
+                                                     (1, 64, 64, 0, (0.4, 100)), (2, 48, 64, 24, (1.0, 3)), (1, 16, 16, 16, None)])  # fmt: skip
 def test_rotation_query_factor_and_padded_heads(dtype, maps, dim, vdim, dims, temp):
     """Positions near and far (float32 angles), every map turned on its first entries only, the query
     factor at the steps of its logarithm, and zeros wherever a head is wider than what it holds;
@@ -113,7 +113,7 @@ def test_rotation_query_factor_and_padded_heads(dtype, maps, dim, vdim, dims, te
     H, G, bs = 3, 2, 4
     hd = max(maps * dim, vdim)
     g = torch.Generator().manual_seed(dim + dims)
-    positions = [0, 1, 2, 5, 6, 7, 126, 127, 128, 1000, 30000]
+    positions = [0, 1, 2, 5, 6, 7, 98, 99, 100, 1000, 30000]
     T = len(positions)
     q, k, v = (rounded(torch.randn(T, n, generator=g)) for n in (H * maps * dim, G * maps * dim, G * vdim))
     rot = dict(base=100.0, dims=dims, scaling=dict(factor=4.0, low=1.0, high=4.0, original=64))
@@ -237,7 +237,7 @@ MIXERS = [
     diff_attention(4, 2, 12, 40, 0.6, 0.3, 10, rot=(100.0, 8, (4.0, 1.0, 4.0, 64))),
     diff_attention(3, 3, 20, 24, 0.35, 0.6, 33, rot=(30.0, 20, None)),
     diff_attention(2, 1, 8, 8, 0.9, 0.1, 1),
-    diff_attention(4, 2, 64, 128, 0.2, 0.4, 16, rot=(10000.0, 32, (8.0, 1.0, 4.0, 128))),
+    diff_attention(4, 2, 64, 128, 0.2, 0.4, 16, rot=(10000.0, 32, (6.0, 1.0, 3.0, 128))),
     diff_attention(4, 1, 32, 64, 0.3, 0.8, None, rot=(500.0, 32, (2.0, 0.001, 0.01, 4096))),
     sink_attention(6, 3, 24, 16, 0.5, temp=(0.7, 7), softcap=5.0),
     sink_attention(4, 4, 12, 20, 0.6),

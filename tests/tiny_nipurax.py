@@ -69,10 +69,10 @@ BLOCK_SIZE_B = 8
 # sizes at which the bfloat16 products and attention run this package's tensor-core kernels; the loop runs the
 # first two layers twice
 NIPURAX_C = _model(704, 256, 2e-6, 0.25, (1021, 211, 13), (0, 2, 2), [
-    diff_attention(4, 2, 64, 128, 0.2, 0.4, 100, rot=(10000.0, 32, (8.0, 1.0, 4.0, 128)), mlp=moe(8, 2, 3, 128, 2.0, 2.0, shared=(192, 1.5))),
+    diff_attention(4, 2, 64, 128, 0.2, 0.4, 100, rot=(10000.0, 32, (6.0, 1.0, 3.0, 128)), mlp=moe(8, 2, 3, 128, 2.0, 2.0, shared=(192, 1.5))),
     sink_attention(8, 2, 128, 128, 0.15, temp=(0.5, 50), softcap=20.0, mlp=moe(6, 0, 2, 64, 1.5, 1.0)),
     sink_attention(4, 1, 64, 64, 0.25, temp=(0.2, 9), softcap=8.0),
-    diff_attention(2, 2, 32, 64, 0.3, 0.7, 16, rot=(500000.0, 32, (2.0, 0.001, 0.01, 4096)), mlp=moe(4, 1, 1, 96, 1.0, 1.5, shared=(64, 1.0))),
+    diff_attention(2, 2, 32, 64, 0.3, 0.7, 16, rot=(400000.0, 32, (2.0, 0.001, 0.01, 4096)), mlp=moe(4, 1, 1, 96, 1.0, 1.5, shared=(64, 1.0))),
 ])  # fmt: skip
 BLOCK_SIZE_C = 16
 
